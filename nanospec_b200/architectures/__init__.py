@@ -1,3 +1,3 @@
-from . import llama  # registers LlamaForCausalLM
+from . import dezolorn, llama  # registers Dezolorn and LlamaForCausalLM
 
-__all__ = ["llama"]
+__all__ = ["dezolorn", "llama"]

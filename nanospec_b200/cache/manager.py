@@ -29,7 +29,7 @@ _P, _I, _L = c_void_p, c_int, c_longlong
 _PI, _PL = POINTER(c_int), POINTER(c_longlong)
 
 _SIGNATURES = {
-    "ns_cache_create": [_I, _PI, _PI, _I, _I, POINTER(c_void_p)],
+    "ns_cache_create": [_I, _PI, _PI, _PI, _I, _I, POINTER(c_void_p)],
     "ns_cache_destroy": [_P],
     "ns_cache_begin": [_P, _L],
     "ns_cache_extend": [_P, _L, _L],
@@ -133,17 +133,21 @@ class CacheManager:
             raise ValueError("a cache needs at least one page, a positive page size and one state slot")
         self.block_size = block_size
         self.num_blocks = num_blocks
-        by_geometry: dict[tuple[int, int, int], list[int]] = {}
+        by_geometry: dict[tuple, list[int]] = {}
         for lane, (need, _) in enumerate(lane_needs):
             if need is not None:
-                by_geometry.setdefault((need.kv_heads, need.head_dim, need.window), []).append(lane)
-        specs = [GroupSpec(tuple(lanes), kvh, hd, block_size, window) for (kvh, hd, window), lanes in by_geometry.items()]
+                keep = need.keep_first if need.window > 0 else 0
+                v_dim = None if need.v_dim in (None, need.head_dim) else need.v_dim
+                by_geometry.setdefault((need.kv_heads, need.head_dim, need.window, keep, v_dim), []).append(lane)
+        specs = [GroupSpec(tuple(lanes), kvh, hd, block_size, window, keep, v_dim)
+                 for (kvh, hd, window, keep, v_dim), lanes in by_geometry.items()]
         self._lib = _native()
         n = len(specs)
         handle = c_void_p()
         self._n_groups = n
         self._status(self._lib.ns_cache_create(n, (c_int * max(n, 1))(*[s.page_size for s in specs]),
-                                               (c_int * max(n, 1))(*[s.window for s in specs]), num_blocks, num_state_slots,
+                                               (c_int * max(n, 1))(*[s.window for s in specs]),
+                                               (c_int * max(n, 1))(*[s.keep_first for s in specs]), num_blocks, num_state_slots,
                                                byref(handle)))
         self._h = handle
         self.groups: list[CacheGroup] = [CacheGroup(self, gi, s, num_blocks) for gi, s in enumerate(specs)]

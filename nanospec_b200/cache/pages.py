@@ -23,6 +23,12 @@ class GroupSpec:
     head_dim: int
     page_size: int
     window: int = 0  # 0: every position is kept; w > 0: a query reads the last w positions only
+    keep_first: int = 0  # with a window: the first so many positions stay readable as well
+    v_dim: int | None = None  # the values' head size when it is not the keys'
+
+    @property
+    def kept_blocks(self) -> int:
+        return -(-self.keep_first // self.page_size) if self.window > 0 else 0
 
     def blocks_for(self, seq_len: int) -> int:
         return -(-seq_len // self.page_size)
@@ -40,7 +46,7 @@ class GroupSpec:
         if self.window <= 0:
             return full
         span = self.window - 1 + max(1, longest_portion)
-        return min(full, self.blocks_for(span) + 1)
+        return min(full, self.blocks_for(span) + 1 + self.kept_blocks)
 
 
 RELEASED = -1  # block-table entry of a page that a window has passed

@@ -18,12 +18,17 @@ class CacheStorage:
                  dtype: torch.dtype, device: torch.device) -> None:
         self.manager = manager
         self.dtype, self.device = dtype, device
-        self.group_kv: list[torch.Tensor] = []
+        self.group_kv: list[torch.Tensor | tuple[torch.Tensor, torch.Tensor]] = []
         for g in manager.groups:
             s = g.spec
             # [lane in group, k|v, page, kv head, offset, dim]: one kv head's tokens of a page are contiguous
-            self.group_kv.append(torch.zeros((len(s.lanes), 2, manager.num_blocks, s.kv_heads, s.page_size, s.head_dim),
-                                             dtype=dtype, device=device))
+            if s.v_dim is None:
+                self.group_kv.append(torch.zeros((len(s.lanes), 2, manager.num_blocks, s.kv_heads, s.page_size, s.head_dim),
+                                                 dtype=dtype, device=device))
+            else:  # values of another width than the keys: a tensor each, [lane in group, page, kv head, offset, dim]
+                self.group_kv.append(tuple(
+                    torch.zeros((len(s.lanes), manager.num_blocks, s.kv_heads, s.page_size, d), dtype=dtype, device=device)
+                    for d in (s.head_dim, s.v_dim)))
         self.state: dict[int, torch.Tensor] = {}
         for lane, (_, st) in enumerate(lane_needs):
             if st is not None:
@@ -32,7 +37,7 @@ class CacheStorage:
         self.lane_needs = lane_needs
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.group_kv) + \
+        return sum(t.numel() * t.element_size() for g in self.group_kv for t in (g if isinstance(g, tuple) else (g,))) + \
             sum(t.numel() * t.element_size() for t in self.state.values())
 
     def lane_views(self, group_tables: list[torch.Tensor | None]) -> list[LaneView]:
@@ -45,7 +50,8 @@ class CacheStorage:
                 continue
             spec = self.manager.groups[gi].spec
             idx = spec.lanes.index(lane)
-            kv = self.group_kv[gi][idx]
+            store = self.group_kv[gi]
+            kv = (store[0][idx], store[1][idx]) if isinstance(store, tuple) else store[idx]
             views.append(LaneView(kv[0], kv[1], group_tables[gi], spec.page_size, spec.window, self.state.get(lane)))
         return views
 

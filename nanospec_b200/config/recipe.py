@@ -39,7 +39,7 @@ class LayerSpec:
     block: str
     prefix: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None  # None: the layer has no feed-forward sublayer
     norm: PartSpec
     names: Mapping[str, str]
 
@@ -55,11 +55,14 @@ class Run:
     `lane` is the cache lane the mixer works on; lanes are numbered by the recipe and a
     lane's geometry comes from the first run that writes it.  A run with `writes=False`
     reads a lane that an earlier run of the same step has written (cache sharing).
+    `add_input`: the embedding's output (the stream as it was before the first run) is added to the
+    stream right before this run - how a pass of a repeated span of layers starts.
     """
 
     layer: int
     lane: int
     writes: bool = True
+    add_input: bool = False
 
 
 @dataclass(frozen=True)

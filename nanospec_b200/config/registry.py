@@ -41,7 +41,9 @@ def registered_architectures() -> list[str]:
 
 def resolve_architecture(cfg: dict[str, Any]) -> Architecture:
     """The entry that a config.json asks for."""
-    names = cfg.get("architectures") or []
+    names = list(cfg.get("architectures") or [])
+    if isinstance(cfg.get("architecture"), str):  # some writers name the one architecture under the singular key
+        names.append(cfg["architecture"])
     for n in names:
         if n in _BY_NAME:
             return _BY_NAME[n]

@@ -7,9 +7,11 @@
 // it for every step; the bfloat16 path uses it for sizes that the tensor-core kernels refuse.
 //
 // A query at position p of request r sees the keys at positions max(0, p - window + 1) .. p
-// of the same request (window == 0: all of 0 .. p).  Keys and values are read from
-// cache[page, kv_head, offset, :] with page = block_table[r, position / page_size]; the
-// step's own keys have been written before this kernel runs.  kv_head = q_head / (nq / nkv).
+// of the same request (window == 0: all of 0 .. p) and, with keep_first > 0, also the keys at
+// positions 0 .. keep_first - 1 however far back they lie (they keep their own positions).  Keys and
+// values are read from cache[page, kv_head, offset, :] with page = block_table[r, position / page_size];
+// the step's own keys have been written before this kernel runs.  kv_head = q_head / (nq / nkv).
+// Keys have d features and values dv (the two caches are separate tensors).
 #include "common.cuh"
 
 namespace {
@@ -21,7 +23,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
                          const T* __restrict__ v_cache, const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ token_req, const int* __restrict__ positions, T* __restrict__ out,
-                         int o_stride, int n_tokens, int nq, int nkv, int d, int page_size, float scale, int window) {
+                         int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size, float scale, int window,
+                         int keep_first) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     extern __shared__ float qsm[];
@@ -29,7 +32,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
     const long long w = (long long)blockIdx.x * kWarpsPerBlock + wib;
     if (w >= (long long)n_tokens * nq) return;
     const int n = (int)(w / nq), h = (int)(w % nq);
-    T* o = out + (size_t)n * o_stride + (size_t)h * d;
+    T* o = out + (size_t)n * o_stride + (size_t)h * dv;
     const int req = token_req[n];
     if (req < 0) return;
     const int pos = positions[n];
@@ -48,9 +51,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
     for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
     const int* bt = block_table + (size_t)req * table_stride;
 
-    for (int kb = kstart; kb < kend; kb += 32) {
+    // two runs of keys: the kept first ones that lie before the window, then the window
+    const int kept_end = min(keep_first, kstart);
+    for (int seg = 0; seg < 2; ++seg) {
+    const int s_lo = seg ? kstart : 0, s_hi = seg ? kend : kept_end;
+    for (int kb = s_lo; kb < s_hi; kb += 32) {
         const int key = kb + lane;
-        const bool valid = key < kend;
+        const bool valid = key < s_hi;
         unsigned slot = 0;
         float s = -INFINITY;
         if (valid) {
@@ -68,40 +75,41 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         l = l * corr + ns_warp_sum(p);
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[i] *= corr;
-        const int cnt = min(32, kend - kb);
+        const int cnt = min(32, s_hi - kb);
         for (int j = 0; j < cnt; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const unsigned sj = __shfl_sync(0xffffffffu, slot, j);
-            const T* vr = v_cache + (size_t)sj * d;
+            const T* vr = v_cache + (size_t)sj * dv;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int e = lane + 32 * i;
-                if (e < d) acc[i] = fmaf(pj, ns_ld(vr, e), acc[i]);
+                if (e < dv) acc[i] = fmaf(pj, ns_ld(vr, e), acc[i]);
             }
         }
         m = m_new;
+    }
     }
     const float inv = 1.f / l;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
         const int e = lane + 32 * i;
-        if (e < d) ns_st(o, e, acc[i] * inv);
+        if (e < dv) ns_st(o, e, acc[i] * inv);
     }
 }
 
 template <typename T>
 int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
            int table_stride, const int* token_req, const int* positions, void* out, int o_stride, int n_tokens, int nq,
-           int nkv, int d, int page_size, float scale, int window, cudaStream_t stream) {
+           int nkv, int d, int dv, int page_size, float scale, int window, int keep_first, cudaStream_t stream) {
     const long long warps = (long long)n_tokens * nq;
     const unsigned blocks = (unsigned)((warps + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
-    const int dpl = (d + 31) / 32;
+    const int dpl = (dv + 31) / 32;
 #define NS_ATTN_CASE(D)                                                                                              \
     case D:                                                                                                          \
         NS_LAUNCH((attention_generic_kernel<T, D>), blocks, kWarpsPerBlock * 32, smem, stream,                                \
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride, token_req,       \
-            positions, (T*)out, o_stride, n_tokens, nq, nkv, d, page_size, scale, window);                           \
+            positions, (T*)out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first);                           \
         break;
     switch (dpl) {
         NS_ATTN_CASE(1) NS_ATTN_CASE(2) NS_ATTN_CASE(3) NS_ATTN_CASE(4)
@@ -116,16 +124,18 @@ int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache
 
 NS_API int ns_attention_generic(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int table_stride, const int* token_req, const int* positions,
-                                void* out, int o_stride, int n_tokens, int nq, int nkv, int d, int page_size,
-                                float scale, int window, int dtype, cudaStream_t stream) {
+                                void* out, int o_stride, int n_tokens, int nq, int nkv, int d, int dv, int page_size,
+                                float scale, int window, int keep_first, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
-    if (d < 1 || d > 256) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: head_dim=%d is outside 1..256", d);
+    if (d < 1 || d > 256 || dv < 1 || dv > 256)
+        NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: head sizes %d (keys) and %d (values) must lie in 1..256", d, dv);
+    if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_generic: window=%d keep_first=%d", window, keep_first);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_generic: %d query heads over %d kv heads", nq, nkv);
     if (dtype == NS_F32)
         return launch<float>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, out,
-                             o_stride, n_tokens, nq, nkv, d, page_size, scale, window, stream);
+                             o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, stream);
     if (dtype == NS_BF16)
         return launch<__nv_bfloat16>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
-                                     out, o_stride, n_tokens, nq, nkv, d, page_size, scale, window, stream);
+                                     out, o_stride, n_tokens, nq, nkv, d, dv, page_size, scale, window, keep_first, stream);
     NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_generic: unknown dtype %d", dtype);
 }

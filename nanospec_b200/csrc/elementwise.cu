@@ -318,3 +318,93 @@ NS_API int ns_swiglu(const void* gate_up, void* out, int n_rows, int inter, int 
     NS_CHECK_LAUNCH("ns_swiglu");
     return NS_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Layer norm without a bias over the residual stream, with the pending branch output added first:
+//   r = resid[row] + branch[row];  mean = sum(r) / H;  var = sum((r - mean)^2) / H  (two passes over the
+//   row, which lies in shared memory);  out = (r - mean) * rsqrt(var + eps) * gain,  all in float.
+// `rows` and `write_resid` as in add_rmsnorm.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
+                     T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    extern __shared__ float ln_row[];
+    __shared__ float scratch[32];
+    const int j = blockIdx.x;
+    const int row = rows ? rows[j] : j;
+    float* r = resid + (size_t)row * hidden;
+    const T* b = branch ? branch + (size_t)row * hidden : nullptr;
+    T* o = out + (size_t)j * hidden;
+    float s = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        float x = r[h];
+        if (b) {
+            x += ns_ld(b, h);
+            if (write_resid) r[h] = x;
+        }
+        ln_row[h] = x;
+        s += x;
+    }
+    const float mean = ns_block_sum(s, scratch) / (float)hidden;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float dlt = ln_row[h] - mean;
+        ss += dlt * dlt;
+    }
+    const float inv = rsqrtf(ns_block_sum(ss, scratch) / (float)hidden + eps);
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) ns_st(o, h, (ln_row[h] - mean) * inv * gain[h]);
+}
+
+template <typename T>
+static int launch_add_layernorm(float* resid, const void* branch, const float* gain, void* out, const int* rows, int n_rows,
+                                int hidden, float eps, int write_resid, cudaStream_t stream) {
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_add_layernorm: a row of %d floats does not fit shared memory", hidden);
+    if (smem > 48 * 1024) {
+        static int raised = 0;  // per instantiation
+        if (raised < (int)smem) {
+            NS_CUDA(cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            raised = 200 * 1024;
+        }
+    }
+    NS_LAUNCH((add_layernorm_kernel<T>), n_rows, 256, smem, stream, resid, (const T*)branch, gain, (T*)out, rows, hidden, eps,
+              write_resid);
+    NS_CHECK_LAUNCH("ns_add_layernorm");
+    return NS_OK;
+}
+
+NS_API int ns_add_layernorm(float* resid, const void* branch, const float* gain, void* out, const int* rows, int n_rows,
+                            int hidden, float eps, int write_resid, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return NS_OK;
+    if (hidden <= 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_add_layernorm: hidden=%d", hidden);
+    if (rows && write_resid) NS_FAIL(NS_ERR_ARGUMENT, "ns_add_layernorm: a row selection cannot write the residual back");
+    if (dtype == NS_F32) return launch_add_layernorm<float>(resid, branch, gain, out, rows, n_rows, hidden, eps, write_resid, stream);
+    if (dtype == NS_BF16)
+        return launch_add_layernorm<__nv_bfloat16>(resid, branch, gain, out, rows, n_rows, hidden, eps, write_resid, stream);
+    NS_FAIL(NS_ERR_ARGUMENT, "ns_add_layernorm: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------------
+// logits in place: x = x * scale, then x = cap * tanh(x / cap) when cap > 0
+// ---------------------------------------------------------------------------------------
+__global__ void scale_softcap_kernel(float* __restrict__ x, int cols, long long stride, float scale, float cap, size_t total) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float* p = x + (i / cols) * stride + (i % cols);
+    float v = *p * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    *p = v;
+}
+
+NS_API int ns_scale_softcap(float* x, int n_rows, int cols, long long stride, float scale, float cap, cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * cols;
+    if (total == 0) return NS_OK;
+    NS_LAUNCH(scale_softcap_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, cols, stride, scale, cap, total);
+    NS_CHECK_LAUNCH("ns_scale_softcap");
+    return NS_OK;
+}

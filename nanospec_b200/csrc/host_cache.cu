@@ -22,6 +22,7 @@ constexpr int kReleased = -1;  // block-table entry of a page that a window has 
 
 struct Group {
     int page_size = 0, window = 0, num_pages = 0;
+    int keep_first = 0;  // with a window: the first so many positions stay readable, so their blocks are never given back
     std::vector<int> free_list;  // back() goes out next
     std::vector<unsigned char> is_free;
 
@@ -32,12 +33,17 @@ struct Group {
         const long long first_pos = len - window + 1;
         return (first_pos > 0 ? first_pos : 0) / page_size;
     }
+    // blocks at the start of a table that a window never passes (they hold the kept first positions)
+    int kept_blocks() const { return window > 0 ? (keep_first + page_size - 1) / page_size : 0; }
 };
 
 struct Table {
     std::vector<int> pages;  // one entry per logical block, kReleased once given back
-    int first_live = 0;
+    int first_live = 0;      // the blocks kept_blocks() .. first_live - 1 have been given back
+    int released(const struct Group& g) const;
 };
+
+inline int Table::released(const Group& g) const { return first_live > g.kept_blocks() ? first_live - g.kept_blocks() : 0; }
 
 struct Request {
     long long seq_len = 0;
@@ -95,7 +101,7 @@ int extend_request(Cache& c, long long id, Request& r, long long n_tokens) {
 int rollback_request(Cache& c, Request& r, long long seq_len) {
     if (seq_len < 0 || seq_len > r.seq_len) NS_FAIL(NS_ERR_INVARIANT, "rollback goes backwards only");
     for (size_t gi = 0; gi < c.groups.size(); ++gi)
-        if (c.groups[gi].blocks_for(seq_len) < r.tables[gi].first_live)
+        if (r.tables[gi].released(c.groups[gi]) > 0 && c.groups[gi].blocks_for(seq_len) < r.tables[gi].first_live)
             NS_FAIL(NS_ERR_INVARIANT, "cannot roll back behind pages that a window has already released");
     for (size_t gi = 0; gi < c.groups.size(); ++gi) {
         Table& t = r.tables[gi];
@@ -115,13 +121,14 @@ int trim_request(Cache& c, Request& r, int* released) {
         Group& g = c.groups[gi];
         Table& t = r.tables[gi];
         const int first = (int)std::min<long long>(g.first_needed_block(r.seq_len), (long long)t.pages.size());
-        for (int i = t.first_live; i < first; ++i) {
+        const int lo = std::max(t.first_live, g.kept_blocks());
+        for (int i = lo; i < first; ++i) {
             const int st = give_page(g, t.pages[i]);
             if (st != NS_OK) return st;
             t.pages[i] = kReleased;
             ++*released;
         }
-        if (first > t.first_live) t.first_live = first;
+        if (first > lo) t.first_live = first;
     }
     return NS_OK;
 }
@@ -135,7 +142,9 @@ inline int pad4(long long n) { return (int)((n + 3) & ~3ll); }
     if (it_ == (c)->live.end()) NS_FAIL(NS_ERR_NOT_LIVE, "request %lld is not live", (long long)(id)); \
     Request& r = it_->second
 
-NS_API int ns_cache_create(int n_groups, const int* page_size, const int* window, int num_pages, int num_slots, void** out) {
+// `keep_first` may be null (no group keeps first positions behind its window)
+NS_API int ns_cache_create(int n_groups, const int* page_size, const int* window, const int* keep_first, int num_pages, int num_slots,
+                           void** out) {
     if (n_groups < 0 || n_groups > 16) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_cache_create: %d cache groups (at most 16)", n_groups);
     if (num_pages <= 0 || num_slots <= 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_cache_create: a pool needs at least one page and one slot");
     Cache* c = new Cache();
@@ -145,6 +154,7 @@ NS_API int ns_cache_create(int n_groups, const int* page_size, const int* window
         if (page_size[gi] <= 0) { delete c; NS_FAIL(NS_ERR_ARGUMENT, "ns_cache_create: page size %d", page_size[gi]); }
         g.page_size = page_size[gi];
         g.window = window[gi];
+        g.keep_first = keep_first ? std::max(keep_first[gi], 0) : 0;
         g.num_pages = num_pages;
         g.free_list.resize(num_pages);
         for (int p = 0; p < num_pages; ++p) g.free_list[p] = num_pages - 1 - p;  // page 0 goes out first
@@ -245,7 +255,7 @@ NS_API int ns_cache_free_pages(void* h, int* out) {
 NS_API int ns_cache_held_pages(void* h, long long id, int* out) {
     Cache* c = as_cache(h);
     NS_FIND(c, id, r);
-    for (size_t gi = 0; gi < c->groups.size(); ++gi) out[gi] = (int)r.tables[gi].pages.size() - r.tables[gi].first_live;
+    for (size_t gi = 0; gi < c->groups.size(); ++gi) out[gi] = (int)r.tables[gi].pages.size() - r.tables[gi].released(c->groups[gi]);
     return NS_OK;
 }
 
@@ -318,7 +328,7 @@ NS_API int ns_cache_check(void* h) {
                         (int)t.pages.size(), kv.second.seq_len);
             for (int i = 0; i < (int)t.pages.size(); ++i) {
                 const int p = t.pages[i];
-                if (i < t.first_live) {
+                if (i >= g.kept_blocks() && i < t.first_live) {
                     if (p != kReleased) NS_FAIL(NS_ERR_INVARIANT, "group %d: request %lld keeps a page behind its window", (int)gi, kv.first);
                     continue;
                 }
@@ -591,7 +601,10 @@ NS_API int ns_step_pack_decode(void* h, int B, int size, const long long* ids, l
             const std::vector<int>& pages = reqs[b]->tables[gi].pages;
             // entries behind a window are never read; the row is written from its first live entry on
             const int first = reqs[b]->tables[gi].first_live;
-            std::copy(pages.begin() + first, pages.end(), buf + table_off[gi] + (long long)b * width + first);
+            const int kept = std::min<int>(c->groups[gi].kept_blocks(), (int)pages.size());
+            if (first > kept) std::copy(pages.begin(), pages.begin() + kept, buf + table_off[gi] + (long long)b * width);
+            std::copy(pages.begin() + (first > kept ? first : 0), pages.end(),
+                      buf + table_off[gi] + (long long)b * width + (first > kept ? first : 0));
         }
     return NS_OK;
 }

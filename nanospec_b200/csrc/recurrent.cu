@@ -1,0 +1,365 @@
+// Mixers with a fixed-size state per request: linear attention with a decay (retention) and the gated
+// delta rule, for portions of prompts and single decoded tokens alike.
+//
+// Per head the state is a matrix S [D, V] of floats.  For every token, in order:
+//     plain:  S = g S + k v^T                      o = S^T q
+//     delta:  S = g S;  u = beta (v - S^T k);  S = S + k u^T;   o = S^T q
+// The columns of S never meet: column e needs only v[e], so the scan runs one column per group of four
+// lanes (each lane holds a quarter of the column's D entries in registers), walks the request's tokens of
+// this step in order, and leaves the state where the next step finds it.  A request's result therefore
+// does not depend on how its tokens were cut into steps: the operations per token are the same.
+//
+// Everything that enters the recurrence is prepared in float by a kernel with one block per token
+// (`*_prepare`): q, k (a head's row padded with zeros to a multiple of 4 * R floats), v, and for the delta
+// rule the decay and the write strength.  A third kernel divides each head's read-out by its root mean
+// square, applies a gain and the output gate, and rounds once.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+template <typename T> __device__ __forceinline__ float round_to(float x);
+template <> __device__ __forceinline__ float round_to<float>(float x) { return x; }
+template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ---------------------------------------------------------------------------------------
+// delta rule, preparation.  proj row: the packed projection [q: G*D | k: G*D | v: H*V | ...] with the
+// write-strength and decay inputs at columns off_b and off_a (H each).  The C = 2*G*D + H*V leading columns
+// pass a causal convolution over time per channel (taps [C, n_taps], the last tap is the current token's;
+// inputs before this step's first token come from the request's tail [(n_taps - 1), C] in its state, which
+// is zero at a sequence's start) and silu; the result is rounded to the activations' type.  Then q and k
+// become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale, and
+//     g = exp(-exp(A_log[h]) * softplus(a + dt_bias[h])),  beta = sigmoid(b).
+// rec row (floats): [q: G*Dp | k: G*Dp | v: H*V | g: H | beta: H].
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const T* __restrict__ proj, int ld_proj, const float* __restrict__ taps, int n_taps,
+                     const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
+                     long long state_floats, long long tail_off, const int* __restrict__ token_req,
+                     const int* __restrict__ qo_indptr, const int* __restrict__ state_slot, float* __restrict__ rec, int ld_rec,
+                     int G, int H, int D, int Dp, int V, int off_b, int off_a, float q_scale, float unit_eps) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    extern __shared__ float ch[];  // the C channels after convolution and silu
+    const int n = blockIdx.x;
+    const int req = token_req[n];
+    if (req < 0) return;
+    const int start = qo_indptr[req], t = n - start;
+    const int C = 2 * G * D + H * V;
+    const float* tail = state + (long long)state_slot[req] * state_floats + tail_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < n_taps; ++j) {
+            const int i = t - (n_taps - 1) + j;
+            const float x = i >= 0 ? ns_ld(proj, (size_t)(start + i) * ld_proj + c) : tail[(size_t)(i + n_taps - 1) * C + c];
+            acc = fmaf(taps[(size_t)c * n_taps + j], x, acc);
+        }
+        ch[c] = round_to<T>(silu_f(acc));
+    }
+    __syncthreads();
+    float* out = rec + (size_t)n * ld_rec;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int hd = warp; hd < 2 * G; hd += nwarp) {  // q heads, then k heads
+        const float* x = ch + hd * D;
+        float ss = 0.f;
+        for (int e = lane; e < D; e += 32) ss += x[e] * x[e];
+        const float inv = rsqrtf(ns_warp_sum(ss) + unit_eps) * (hd < G ? q_scale : 1.f);
+        float* o = out + (size_t)hd * Dp;
+        for (int e = lane; e < Dp; e += 32) o[e] = e < D ? x[e] * inv : 0.f;
+    }
+    float* ov = out + (size_t)2 * G * Dp;
+    for (int e = threadIdx.x; e < H * V; e += blockDim.x) ov[e] = ch[2 * G * D + e];
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float a = ns_ld(proj, (size_t)n * ld_proj + off_a + h) + dt_bias[h];
+        const float b = ns_ld(proj, (size_t)n * ld_proj + off_b + h);
+        ov[H * V + h] = expf(-expf(a_log[h]) * softplus_f(a));
+        ov[H * V + H + h] = 1.f / (1.f + expf(-b));
+    }
+}
+
+// After the preparation: the tail of every request moves on by the tokens of this step.
+// new tail[j] = the input at (L - (n_taps - 1) + j) of the step's L tokens, or the old tail[j + L] before them.
+template <typename T>
+__global__ void conv_tail_kernel(const T* __restrict__ proj, int ld_proj, float* __restrict__ state, long long state_floats,
+                                 long long tail_off, const int* __restrict__ qo_indptr, const int* __restrict__ state_slot,
+                                 int C, int n_taps) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int start = qo_indptr[b], L = qo_indptr[b + 1] - start;
+    if (L <= 0) return;
+    float* tail = state + (long long)state_slot[b] * state_floats + tail_off;
+    for (int j = 0; j < n_taps - 1; ++j) {  // ascending: entry j + L is read before it is written
+        const int i = L - (n_taps - 1) + j;
+        tail[(size_t)j * C + c] = i >= 0 ? ns_ld(proj, (size_t)(start + i) * ld_proj + c) : tail[(size_t)(j + L) * C + c];
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// linear attention, preparation.  proj row: [q: H*D | k: H*D | v: H*V | ...].  q and k are rotated by the
+// token's position on the first 2 * rot_pairs features of each head (interleaved = 1: pairs (2i, 2i+1); 0:
+// pairs (i, i + rot_pairs); angle = float(position) * inv_freq[i]; cos and sin times `magnitude`), then k is
+// multiplied by k_scale and q by q_scale.  rec row (floats): [q: H*Dp | k: H*Dp | v: H*V].
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotary_prepare_kernel(const T* __restrict__ proj, int ld_proj, const int* __restrict__ positions, const int* __restrict__ token_req,
+                      const float* __restrict__ inv_freq, float magnitude, int interleaved, int rot_pairs, float* __restrict__ rec,
+                      int ld_rec, int H, int D, int Dp, int V, float q_scale, float k_scale) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int n = blockIdx.x;
+    if (token_req[n] < 0) return;
+    const float fpos = (float)positions[n];
+    const T* row = proj + (size_t)n * ld_proj;
+    float* out = rec + (size_t)n * ld_rec;
+    const int units = rot_pairs + (Dp - 2 * rot_pairs);
+    for (int w = threadIdx.x; w < 2 * H * units; w += blockDim.x) {
+        const int hd = w / units, u = w - hd * units;  // q heads, then k heads
+        const float scale = hd < H ? q_scale : k_scale;
+        const T* x = row + (size_t)hd * D;
+        float* o = out + (size_t)hd * Dp;
+        if (u < rot_pairs) {
+            const int e0 = interleaved ? 2 * u : u, e1 = interleaved ? 2 * u + 1 : u + rot_pairs;
+            const float a = ns_ld(x, e0), b = ns_ld(x, e1);
+            float sn, cs;
+            sincosf(fpos * inv_freq[u], &sn, &cs);
+            sn *= magnitude; cs *= magnitude;
+            o[e0] = (a * cs - b * sn) * scale;
+            o[e1] = (b * cs + a * sn) * scale;
+        } else {
+            const int e = 2 * rot_pairs + (u - rot_pairs);
+            o[e] = e < D ? ns_ld(x, e) * scale : 0.f;
+        }
+    }
+    float* ov = out + (size_t)2 * H * Dp;
+    for (int e = threadIdx.x; e < H * V; e += blockDim.x) ov[e] = ns_ld(row, (size_t)2 * H * D + e);
+}
+
+// ---------------------------------------------------------------------------------------
+// the scan.  grid (request, head, 32 columns); 128 threads: lane = part * 8 + column, part 0..3 holds rows
+// part*R .. part*R + R - 1 of its column.  q and k heads are shared by H / G heads each.
+// gate: per token and head (row stride ld) or null, then `decay[h]` is used; beta: null selects the plain rule.
+// ---------------------------------------------------------------------------------------
+template <int R>
+__device__ __forceinline__ void load_row(const float* p, float (&x)[R]) {
+#pragma unroll
+    for (int i = 0; i < R / 4; ++i) {
+        const float4 f = reinterpret_cast<const float4*>(p)[i];
+        x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+    }
+}
+
+template <int R>
+__device__ __forceinline__ float dot_row(const float (&s)[R], const float (&x)[R]) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // four partial sums, always combined in the same order
+#pragma unroll
+    for (int i = 0; i < R; i += 4) {
+        a0 = fmaf(s[i], x[i], a0); a1 = fmaf(s[i + 1], x[i + 1], a1);
+        a2 = fmaf(s[i + 2], x[i + 2], a2); a3 = fmaf(s[i + 3], x[i + 3], a3);
+    }
+    float v = (a0 + a1) + (a2 + a3);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    return v;
+}
+
+template <int R>
+__global__ void __launch_bounds__(128)
+linear_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                   const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ decay, int ld,
+                   float* __restrict__ state, long long state_floats, const int* __restrict__ qo_indptr,
+                   const int* __restrict__ state_slot, float* __restrict__ out, int ld_out, int H, int G, int D, int V) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = lane >> 3;
+    const int e = blockIdx.z * 32 + warp * 8 + (lane & 7);
+    const bool active = e < V;
+    const int start = qo_indptr[b], end = qo_indptr[b + 1];
+    if (end <= start) return;
+    constexpr int Dp = 4 * R;
+    const int hk = h / (H / G);
+    float* S_mem = state + (long long)state_slot[b] * state_floats + ((long long)h * D + part * R) * V + e;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[r] = (active && part * R + r < D) ? S_mem[(size_t)r * V] : 0.f;
+    const float* qp = q + (size_t)hk * Dp + part * R;
+    const float* kp = k + (size_t)hk * Dp + part * R;
+    const float fixed = decay ? decay[h] : 1.f;
+    constexpr bool kAhead = R <= 32;  // wider heads would not keep two tokens' operands in registers
+    constexpr int RN = kAhead ? R : 4;
+    float kn[RN], qn[RN], vn = 0.f, gn = fixed, bn = 0.f;
+    if (kAhead) {
+        load_row<RN>(kp + (size_t)start * ld, kn);
+        load_row<RN>(qp + (size_t)start * ld, qn);
+        vn = active ? v[(size_t)start * ld + h * V + e] : 0.f;
+        if (gate) gn = gate[(size_t)start * ld + h];
+        if (beta) bn = beta[(size_t)start * ld + h];
+    }
+    for (int n = start; n < end; ++n) {
+        float kc[R], qc[R];
+        float vc, gc, bc;
+        if (kAhead) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) { kc[r] = kn[r % RN]; qc[r] = qn[r % RN]; }
+            vc = vn; gc = gn; bc = bn;
+            if (n + 1 < end) {  // the next token's operands travel while this one is computed
+                load_row<RN>(kp + (size_t)(n + 1) * ld, kn);
+                load_row<RN>(qp + (size_t)(n + 1) * ld, qn);
+                vn = active ? v[(size_t)(n + 1) * ld + h * V + e] : 0.f;
+                if (gate) gn = gate[(size_t)(n + 1) * ld + h];
+                if (beta) bn = beta[(size_t)(n + 1) * ld + h];
+            }
+        } else {
+            load_row<R>(kp + (size_t)n * ld, kc);
+            load_row<R>(qp + (size_t)n * ld, qc);
+            vc = active ? v[(size_t)n * ld + h * V + e] : 0.f;
+            gc = gate ? gate[(size_t)n * ld + h] : fixed;
+            bc = beta ? beta[(size_t)n * ld + h] : 0.f;
+        }
+        if (beta) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) S[r] *= gc;
+            const float u = bc * (vc - dot_row<R>(S, kc));
+#pragma unroll
+            for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], u, S[r]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], vc, gc * S[r]);
+        }
+        const float o = dot_row<R>(S, qc);
+        if (active && part == 0) out[(size_t)n * ld_out + h * V + e] = o;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+        if (active && part * R + r < D) S_mem[(size_t)r * V] = S[r];
+}
+
+// ---------------------------------------------------------------------------------------
+// read-out to mixer output: per (token, head) o / sqrt(mean(o^2) + eps) * gain[e] (gain may be null)
+// * silu(gate[token, h*V + e]); one warp per (token, head), rounded once to T.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, int ld_o, const T* __restrict__ gate, int ld_gate,
+                                      const float* __restrict__ gain, float eps, T* __restrict__ out, int ld_out,
+                                      const int* __restrict__ token_req, int n_tokens, int H, int V) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)n_tokens * H) return;
+    const int n = (int)(w / H), h = (int)(w % H), lane = threadIdx.x & 31;
+    if (token_req[n] < 0) return;
+    const float* x = o + (size_t)n * ld_o + (size_t)h * V;
+    float ss = 0.f;
+    for (int e = lane; e < V; e += 32) ss += x[e] * x[e];
+    const float inv = rsqrtf(ns_warp_sum(ss) / (float)V + eps);
+    for (int e = lane; e < V; e += 32) {
+        float y = x[e] * inv;
+        if (gain) y *= gain[e];
+        if (gate) y *= silu_f(ns_ld(gate, (size_t)n * ld_gate + (size_t)h * V + e));
+        ns_st(out, (size_t)n * ld_out + (size_t)h * V + e, y);
+    }
+}
+
+}  // namespace
+
+NS_API int ns_delta_prepare(const void* proj, int ld_proj, const float* taps, int n_taps, const float* a_log, const float* dt_bias,
+                            float* state, long long state_floats, long long tail_off, const int* token_req, const int* qo_indptr,
+                            const int* state_slot, float* rec, int ld_rec, int n_tokens, int n_requests, int G, int H, int D, int Dp,
+                            int V, int off_b, int off_a, float q_scale, float unit_eps, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    if (n_taps < 1 || G < 1 || H % G || Dp < D || Dp % 4) NS_FAIL(NS_ERR_ARGUMENT, "ns_delta_prepare: taps=%d heads=%d/%d D=%d Dp=%d", n_taps, H, G, D, Dp);
+    const int C = 2 * G * D + H * V;
+    const size_t smem = (size_t)C * sizeof(float);
+    if (smem > 200 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_delta_prepare: %d channels do not fit shared memory", C);
+    if (dtype != NS_F32 && dtype != NS_BF16) NS_FAIL(NS_ERR_ARGUMENT, "ns_delta_prepare: unknown dtype %d", dtype);
+    if (smem > 48 * 1024) {
+        if (dtype == NS_F32) NS_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        else NS_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    }
+    const dim3 tail_grid(n_requests, (C + 255) / 256);
+    if (dtype == NS_F32) {
+        NS_LAUNCH((delta_prepare_kernel<float>), n_tokens, 256, smem, stream, (const float*)proj, ld_proj, taps, n_taps, a_log, dt_bias,
+                  state, state_floats, tail_off, token_req, qo_indptr, state_slot, rec, ld_rec, G, H, D, Dp, V, off_b, off_a, q_scale, unit_eps);
+        if (n_taps > 1)
+            NS_LAUNCH((conv_tail_kernel<float>), tail_grid, 256, 0, stream, (const float*)proj, ld_proj, state, state_floats, tail_off,
+                      qo_indptr, state_slot, C, n_taps);
+    } else {
+        NS_LAUNCH((delta_prepare_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)proj, ld_proj, taps, n_taps, a_log,
+                  dt_bias, state, state_floats, tail_off, token_req, qo_indptr, state_slot, rec, ld_rec, G, H, D, Dp, V, off_b, off_a, q_scale, unit_eps);
+        if (n_taps > 1)
+            NS_LAUNCH((conv_tail_kernel<__nv_bfloat16>), tail_grid, 256, 0, stream, (const __nv_bfloat16*)proj, ld_proj, state, state_floats,
+                      tail_off, qo_indptr, state_slot, C, n_taps);
+    }
+    NS_CHECK_LAUNCH("ns_delta_prepare");
+    return NS_OK;
+}
+
+NS_API int ns_rotary_prepare(const void* proj, int ld_proj, const int* positions, const int* token_req, const float* inv_freq,
+                             float magnitude, int interleaved, int rot_pairs, float* rec, int ld_rec, int n_tokens, int H, int D,
+                             int Dp, int V, float q_scale, float k_scale, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    if (rot_pairs < 0 || 2 * rot_pairs > D || Dp < D || Dp % 4) NS_FAIL(NS_ERR_ARGUMENT, "ns_rotary_prepare: %d pairs, D=%d, Dp=%d", rot_pairs, D, Dp);
+    if (dtype == NS_F32)
+        NS_LAUNCH((rotary_prepare_kernel<float>), n_tokens, 256, 0, stream, (const float*)proj, ld_proj, positions, token_req, inv_freq,
+                  magnitude, interleaved, rot_pairs, rec, ld_rec, H, D, Dp, V, q_scale, k_scale);
+    else if (dtype == NS_BF16)
+        NS_LAUNCH((rotary_prepare_kernel<__nv_bfloat16>), n_tokens, 256, 0, stream, (const __nv_bfloat16*)proj, ld_proj, positions, token_req,
+                  inv_freq, magnitude, interleaved, rot_pairs, rec, ld_rec, H, D, Dp, V, q_scale, k_scale);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_rotary_prepare: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_rotary_prepare");
+    return NS_OK;
+}
+
+// Rows per lane that the scan is compiled for; a head of D features takes the smallest R with 4 * R >= D.
+NS_API int ns_linear_scan_rows(int D) {
+    for (int r : {4, 8, 16, 32, 64})
+        if (4 * r >= D) return r;
+    return 0;
+}
+
+NS_API int ns_linear_scan(const float* q, const float* k, const float* v, const float* gate, const float* beta, const float* decay,
+                          int ld, float* state, long long state_floats, const int* qo_indptr, const int* state_slot, float* out,
+                          int ld_out, int n_requests, int H, int G, int D, int V, cudaStream_t stream) {
+    if (n_requests <= 0) return NS_OK;
+    const int R = ns_linear_scan_rows(D);
+    if (!R) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: a head of %d features (at most 256)", D);
+    if (G < 1 || H % G) NS_FAIL(NS_ERR_ARGUMENT, "ns_linear_scan: %d heads over %d key heads", H, G);
+    if (!gate && !decay) NS_FAIL(NS_ERR_ARGUMENT, "ns_linear_scan: neither a gate per token nor a decay per head");
+    if (ld % 4 || ((uintptr_t)q | (uintptr_t)k) % 16) NS_FAIL(NS_ERR_ARGUMENT, "ns_linear_scan: q and k rows must be 16-byte aligned");
+    if (H > 65535 || (V + 31) / 32 > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: %d heads of %d columns exceed the grid", H, V);
+    const dim3 grid(n_requests, H, (V + 31) / 32);
+#define NS_SCAN_CASE(RR)                                                                                                        \
+    case RR:                                                                                                                    \
+        NS_LAUNCH((linear_scan_kernel<RR>), grid, 128, 0, stream, q, k, v, gate, beta, decay, ld, state, state_floats, qo_indptr, \
+                  state_slot, out, ld_out, H, G, D, V);                                                                         \
+        break;
+    switch (R) { NS_SCAN_CASE(4) NS_SCAN_CASE(8) NS_SCAN_CASE(16) NS_SCAN_CASE(32) NS_SCAN_CASE(64) }
+#undef NS_SCAN_CASE
+    NS_CHECK_LAUNCH("ns_linear_scan");
+    return NS_OK;
+}
+
+NS_API int ns_head_norm_gate(const float* o, int ld_o, const void* gate, int ld_gate, const float* gain, float eps, void* out,
+                             int ld_out, const int* token_req, int n_tokens, int H, int V, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    const long long warps = (long long)n_tokens * H;
+    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    if (dtype == NS_F32)
+        NS_LAUNCH((head_norm_gate_kernel<float>), blocks, 128, 0, stream, o, ld_o, (const float*)gate, ld_gate, gain, eps, (float*)out,
+                  ld_out, token_req, n_tokens, H, V);
+    else if (dtype == NS_BF16)
+        NS_LAUNCH((head_norm_gate_kernel<__nv_bfloat16>), blocks, 128, 0, stream, o, ld_o, (const __nv_bfloat16*)gate, ld_gate, gain, eps,
+                  (__nv_bfloat16*)out, ld_out, token_req, n_tokens, H, V);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_head_norm_gate: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_head_norm_gate");
+    return NS_OK;
+}

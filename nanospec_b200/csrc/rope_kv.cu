@@ -213,3 +213,110 @@ NS_API int ns_rope_kv_write(void* qkv, const int* positions, const int* token_re
     NS_CHECK_LAUNCH("ns_rope_kv_write");
     return NS_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// The general form: an optional RMS norm of the whole q projection and of the whole k projection
+// (one statistic over all heads' features, a gain per feature), then a rotation of the first
+// 2 * rot_pairs features of every q and k head, then the cache write.
+//   pairing: interleaved = 1 turns (2i, 2i+1), 0 turns (i, i + rot_pairs)
+//   angle = float(position) * inv_freq[i]; cos and sin are multiplied by `magnitude`
+// A row of `qkv` is [q: nq*d | k: nkv*d | v: nkv*dv]; q and k are rewritten in place, k and v go to
+// cache[page, kv head, offset, :] (keys d wide, values dv wide) when write_kv.  One block per token;
+// everything is computed in float and rounded once.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                          const int* __restrict__ token_req, const int* __restrict__ block_table, int table_stride,
+                          const float* __restrict__ inv_freq, float magnitude, int interleaved, int rot_pairs,
+                          const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                          T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int nq, int nkv, int d, int dv,
+                          int write_kv) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    __shared__ float scratch[32];
+    const int n = blockIdx.x;
+    const int req = token_req[n];
+    if (req < 0) return;
+    const int pos = positions[n];
+    T* row = qkv + (size_t)n * row_stride;
+    const int q_size = nq * d, k_size = nkv * d;
+    float inv_q = 1.f, inv_k = 1.f;
+    if (q_gain) {
+        float ss = 0.f;
+        for (int e = threadIdx.x; e < q_size; e += blockDim.x) { const float x = ns_ld(row, e); ss += x * x; }
+        inv_q = rsqrtf(ns_block_sum(ss, scratch) / (float)q_size + eps);
+    }
+    if (k_gain) {
+        float ss = 0.f;
+        for (int e = threadIdx.x; e < k_size; e += blockDim.x) { const float x = ns_ld(row, q_size + e); ss += x * x; }
+        inv_k = rsqrtf(ns_block_sum(ss, scratch) / (float)k_size + eps);
+    }
+    size_t slot = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)req * table_stride + pos / page_size];
+        slot = (size_t)page * nkv * page_size + (size_t)(pos % page_size);  // + kv head * page_size
+    }
+    const float fpos = (float)pos;
+    const int units = rot_pairs + (d - 2 * rot_pairs);  // per head: the pairs, then the features that pass
+    for (int w = threadIdx.x; w < (nq + nkv) * units; w += blockDim.x) {
+        const int h = w / units, u = w - h * units;
+        const bool is_k = h >= nq;
+        const int base = h * d;  // q heads and k heads lie one after another in the row
+        const float* gain = is_k ? k_gain : q_gain;
+        const int goff = is_k ? base - q_size : base;
+        const float inv = is_k ? inv_k : inv_q;
+        T* kc = (is_k && write_kv) ? k_cache + (slot + (size_t)(h - nq) * page_size) * d : nullptr;
+        if (u < rot_pairs) {
+            const int e0 = interleaved ? 2 * u : u, e1 = interleaved ? 2 * u + 1 : u + rot_pairs;
+            float a = ns_ld(row, base + e0), b = ns_ld(row, base + e1);
+            if (gain) { a = a * inv * gain[goff + e0]; b = b * inv * gain[goff + e1]; }
+            float sn, cs;
+            sincosf(fpos * inv_freq[u], &sn, &cs);
+            sn *= magnitude; cs *= magnitude;
+            const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+            ns_st(row, base + e0, ra); ns_st(row, base + e1, rb);
+            if (kc) { ns_st(kc, e0, ra); ns_st(kc, e1, rb); }
+        } else {
+            const int e = 2 * rot_pairs + (u - rot_pairs);
+            float a = ns_ld(row, base + e);
+            if (gain) a = a * inv * gain[goff + e];
+            ns_st(row, base + e, a);
+            if (kc) ns_st(kc, e, a);
+        }
+    }
+    if (write_kv) {
+        const T* v = row + q_size + k_size;
+        for (int w = threadIdx.x; w < nkv * dv; w += blockDim.x) {
+            const int h = w / dv, e = w - h * dv;
+            v_cache[(slot + (size_t)h * page_size) * dv + e] = v[w];
+        }
+    }
+}
+
+}  // namespace
+
+NS_API int ns_qk_norm_rope_store(void* qkv, int row_stride, const int* positions, const int* token_req, const int* block_table,
+                                 int table_stride, const float* inv_freq, float magnitude, int interleaved, int rot_pairs,
+                                 const float* q_gain, const float* k_gain, float eps, void* k_cache, void* v_cache,
+                                 int page_size, int nq, int nkv, int d, int dv, int n_tokens, int write_kv, int dtype,
+                                 cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    if (rot_pairs < 0 || 2 * rot_pairs > d) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_qk_norm_rope_store: %d pairs in a head of %d", rot_pairs, d);
+    if (rot_pairs > 0 && !inv_freq) NS_FAIL(NS_ERR_ARGUMENT, "ns_qk_norm_rope_store: no frequencies");
+    if (write_kv && (!k_cache || !v_cache || !block_table)) NS_FAIL(NS_ERR_ARGUMENT, "ns_qk_norm_rope_store: no cache to write");
+    if (dtype == NS_F32)
+        NS_LAUNCH((qk_norm_rope_store_kernel<float>), n_tokens, 256, 0, stream, (float*)qkv, row_stride, positions, token_req,
+                  block_table, table_stride, inv_freq, magnitude, interleaved, rot_pairs, q_gain, k_gain, eps, (float*)k_cache,
+                  (float*)v_cache, page_size, nq, nkv, d, dv, write_kv);
+    else if (dtype == NS_BF16)
+        NS_LAUNCH((qk_norm_rope_store_kernel<__nv_bfloat16>), n_tokens, 256, 0, stream, (__nv_bfloat16*)qkv, row_stride, positions,
+                  token_req, block_table, table_stride, inv_freq, magnitude, interleaved, rot_pairs, q_gain, k_gain, eps,
+                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, nq, nkv, d, dv, write_kv);
+    else
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_qk_norm_rope_store: unknown dtype %d", dtype);
+    NS_CHECK_LAUNCH("ns_qk_norm_rope_store");
+    return NS_OK;
+}

@@ -34,7 +34,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
-    ap.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
     args = ap.parse_args(argv)
     if 64 % args.block_size:
         ap.error("--block-size must divide 64")

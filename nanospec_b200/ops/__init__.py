@@ -433,9 +433,11 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch: t
 
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                       token_req: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, nq: int, nkv: int,
-                      head_dim: int, page_size: int, scale: float | None = None, window: int = 0) -> torch.Tensor:
+                      head_dim: int, page_size: int, scale: float | None = None, window: int = 0,
+                      keep_first: int = 0, v_dim: int | None = None) -> torch.Tensor:
     """q: [N, >= nq*head_dim] rows (a view into the packed projection is fine, unit inner
-    stride); out: [N, nq*head_dim].  See csrc/attention_generic.cu for the masking rule."""
+    stride); out: [N, nq*v_dim] (`v_dim`: the values' head size when it differs from the keys').  `keep_first`: the
+    first so many keys of a request stay visible behind the window.  See csrc/attention_generic.cu for the masking rule."""
     _cuda(q, k_cache, v_cache, block_table, token_req, positions, out)
     _i32(positions, "positions"), _i32(token_req, "token_req")
     n = out.shape[0]
@@ -447,8 +449,8 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         scale = 1.0 / math.sqrt(head_dim)
     lib.call("ns_attention_generic", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(), positions.data_ptr(),
-             out.data_ptr(), out.stride(0), n, nq, nkv, head_dim, page_size, float(scale), int(window),
-             dtype_code(q.dtype), _stream())
+             out.data_ptr(), out.stride(0), n, nq, nkv, head_dim, int(v_dim or head_dim), page_size, float(scale), int(window),
+             int(keep_first), dtype_code(q.dtype), _stream())
     return out
 
 
@@ -628,15 +630,17 @@ def _attention_plan(ctx) -> dict:
 
 
 def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-              window: int = 0) -> torch.Tensor:
+              window: int = 0, keep_first: int = 0, v_dim: int | None = None) -> torch.Tensor:
     """Attention of the step's queries (the first nq*head_dim columns of `qkv`) over `lane`.
 
     bfloat16 with a head size that the tensor-core kernels take: the decode kernel for requests
     that bring one token, the prefill kernel for the others.  float32, and head sizes those
     kernels refuse: the exact kernel, one warp per (token, head)."""
-    if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64:
+    v_dim = head_dim if v_dim is None else v_dim
+    if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64 or v_dim != head_dim or (keep_first and window):
+        # (kept first keys behind a window, and values of another size than the keys, are the exact kernel's alone)
         return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
-                                 head_dim, lane.page_size, scale, window)
+                                 head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim)
     _cuda(qkv, out, lane.k, lane.v, lane.block_table)
     if out.stride(1) != 1 or qkv.stride(1) != 1 or lane.k.dtype != qkv.dtype:
         raise KernelError("attention: row-major bfloat16 operands and a bfloat16 cache are needed")
@@ -683,3 +687,138 @@ def _side_events(device: torch.device):
         ev = _side[(device, "events")] = (torch.cuda.Event(), torch.cuda.Event())
     return ev
 
+
+
+# ---- parts that other architectures add: a centred norm, a general rotation, mixers with a state -------------------
+
+def add_layernorm(resid: torch.Tensor, branch: torch.Tensor | None, gain: torch.Tensor, eps: float, out: torch.Tensor,
+                  rows: torch.Tensor | None = None, write_resid: bool = True) -> torch.Tensor:
+    """resid (+= branch); out = (resid - mean) * rsqrt(var + eps) * gain, statistics in float32 over two passes.
+    `rows` as in `add_rmsnorm`."""
+    _cuda(resid, branch, gain, out, rows)
+    _i32(rows, "rows")
+    hidden, n_rows = resid.shape[1], out.shape[0]
+    if resid.dtype != torch.float32 or gain.dtype != torch.float32:
+        raise KernelError("add_layernorm: the residual stream and the gain are float32")
+    if not (resid.is_contiguous() and out.is_contiguous() and gain.is_contiguous()) or out.shape[1] != hidden \
+            or gain.numel() != hidden:
+        raise KernelError("add_layernorm: operands must be contiguous and agree on the width")
+    if branch is not None and (branch.dtype != out.dtype or branch.shape != resid.shape or not branch.is_contiguous()):
+        raise KernelError("add_layernorm: the branch must match the residual's shape and the output's dtype")
+    if rows is None and n_rows != resid.shape[0]:
+        raise KernelError("add_layernorm: out and resid differ in rows")
+    if rows is not None:
+        if rows.numel() != n_rows:
+            raise KernelError("add_layernorm: one row index per output row")
+        write_resid = False
+    lib.call("ns_add_layernorm", resid.data_ptr(), _ptr(branch), gain.data_ptr(), out.data_ptr(), _ptr(rows), n_rows,
+             hidden, float(eps), int(bool(write_resid)), dtype_code(out.dtype), _stream())
+    return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place on float32 rows: x * scale, then cap * tanh(x / cap) when cap > 0."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("scale_softcap: float32 rows")
+    lib.call("ns_scale_softcap", logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), float(scale),
+             float(cap), _stream())
+    return logits
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, ctx, lane, inv_freq: torch.Tensor | None, magnitude: float, interleaved: bool,
+                       nq: int, nkv: int, head_dim: int, v_dim: int, q_gain: torch.Tensor | None = None,
+                       k_gain: torch.Tensor | None = None, eps: float = 0.0, write_kv: bool = True) -> None:
+    """Rows [q: nq*head_dim | k: nkv*head_dim | v: nkv*v_dim]: an RMS norm of the whole q and of the whole k projection
+    (when gains are given), a rotation of the first 2 * len(inv_freq) features of each head (pairs (2i, 2i+1) when
+    `interleaved`, (i, i + len) otherwise; cos and sin times `magnitude`), q and k rewritten in place, k and v stored at
+    the tokens' cache slots when `write_kv` (csrc/rope_kv.cu)."""
+    _cuda(qkv, inv_freq, q_gain, k_gain)
+    n = qkv.shape[0]
+    if qkv.stride(1) != 1 or qkv.shape[1] < nq * head_dim + nkv * (head_dim + v_dim):
+        raise KernelError("qk_norm_rope_store: rows of [q | k | v] with unit inner stride")
+    for t, name in ((inv_freq, "inv_freq"), (q_gain, "q_gain"), (k_gain, "k_gain")):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError(f"qk_norm_rope_store: {name} must be contiguous float32")
+    if write_kv:
+        if lane.k is None or lane.k.dtype != qkv.dtype or lane.v.dtype != qkv.dtype or not (lane.k.is_contiguous() and lane.v.is_contiguous()):
+            raise KernelError("qk_norm_rope_store: cache pages must be contiguous and of the activations' dtype")
+        if lane.k.shape[-1] != head_dim or lane.v.shape[-1] != v_dim:
+            raise KernelError("qk_norm_rope_store: the cache's head sizes are not the mixer's")
+    bt = lane.block_table if write_kv else None
+    lib.call("ns_qk_norm_rope_store", qkv.data_ptr(), qkv.stride(0), ctx.positions.data_ptr(), ctx.token_req.data_ptr(),
+             _ptr(bt), bt.stride(0) if bt is not None else 0, _ptr(inv_freq), float(magnitude), int(bool(interleaved)),
+             inv_freq.numel() if inv_freq is not None else 0, _ptr(q_gain), _ptr(k_gain), float(eps),
+             _ptr(lane.k) if write_kv else None, _ptr(lane.v) if write_kv else None, lane.page_size, nq, nkv, head_dim, v_dim, n,
+             int(bool(write_kv)), dtype_code(qkv.dtype), _stream())
+
+
+def scan_padded_dim(head_dim: int) -> int:
+    """The width that a head of `head_dim` features is padded to in the scan's float32 operands (csrc/recurrent.cu)."""
+    for r in (4, 8, 16, 32, 64):
+        if 4 * r >= head_dim:
+            return 4 * r
+    raise KernelError(f"a state mixer's heads hold at most 256 features, not {head_dim}")
+
+
+def delta_prepare(proj: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+                  tail_off: int, ctx, rec: torch.Tensor, kv_heads: int, heads: int, head_dim: int, v_dim: int, off_b: int,
+                  off_a: int, q_scale: float, unit_eps: float) -> None:
+    """Short convolution + silu over the leading channels of `proj`, unit q and k, decay and write strength, into the
+    float32 rows of `rec`; then every request's convolution tail (in `state` at `tail_off`) moves on by this step's tokens."""
+    _cuda(proj, taps, a_log, dt_bias, state, rec)
+    if rec.dtype != torch.float32 or state.dtype != torch.float32 or taps.dtype != torch.float32 or not taps.is_contiguous() \
+            or proj.stride(1) != 1 or rec.stride(1) != 1 or not state.is_contiguous():
+        raise KernelError("delta_prepare: float32 taps, state and output; row-major operands")
+    lib.call("ns_delta_prepare", proj.data_ptr(), proj.stride(0), taps.data_ptr(), taps.shape[1], a_log.data_ptr(), dt_bias.data_ptr(),
+             state.data_ptr(), state.stride(0), int(tail_off), ctx.token_req.data_ptr(), ctx.qo_indptr.data_ptr(),
+             ctx.state_slot.data_ptr(), rec.data_ptr(), rec.stride(0), proj.shape[0], ctx.n_requests, kv_heads, heads, head_dim,
+             scan_padded_dim(head_dim), v_dim, off_b, off_a, float(q_scale), float(unit_eps), dtype_code(proj.dtype), _stream())
+
+
+def rotary_prepare(proj: torch.Tensor, ctx, inv_freq: torch.Tensor | None, magnitude: float, interleaved: bool, rec: torch.Tensor,
+                   heads: int, head_dim: int, v_dim: int, q_scale: float, k_scale: float) -> None:
+    """Rows [q: heads*head_dim | k: heads*head_dim | v: heads*v_dim | ...] of `proj`: q and k rotated by position and scaled, all
+    three as float32 into `rec` (heads padded to `scan_padded_dim`)."""
+    _cuda(proj, inv_freq, rec)
+    if rec.dtype != torch.float32 or proj.stride(1) != 1 or rec.stride(1) != 1:
+        raise KernelError("rotary_prepare: float32 output, row-major operands")
+    lib.call("ns_rotary_prepare", proj.data_ptr(), proj.stride(0), ctx.positions.data_ptr(), ctx.token_req.data_ptr(), _ptr(inv_freq),
+             float(magnitude), int(bool(interleaved)), inv_freq.numel() if inv_freq is not None else 0, rec.data_ptr(), rec.stride(0),
+             proj.shape[0], heads, head_dim, scan_padded_dim(head_dim), v_dim, float(q_scale), float(k_scale), dtype_code(proj.dtype),
+             _stream())
+
+
+def linear_scan(rec: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, v_dim: int,
+                decay: torch.Tensor | None = None, gated: bool = False) -> torch.Tensor:
+    """The recurrence over each request's tokens of this step (csrc/recurrent.cu).  `rec` rows: [q: kv_heads*Dp | k: kv_heads*Dp |
+    v: heads*v_dim] and, when `gated` (the delta rule), [g: heads | beta: heads] after them; otherwise `decay` [heads] float32.
+    `state` [slots, floats] holds S [heads, head_dim, v_dim] at the start of each slot's row; `out` [N, heads*v_dim] float32."""
+    _cuda(rec, state, out, decay)
+    dp = scan_padded_dim(head_dim)
+    off_v = 2 * kv_heads * dp
+    need = off_v + heads * v_dim + (2 * heads if gated else 0)
+    if rec.dtype != torch.float32 or out.dtype != torch.float32 or state.dtype != torch.float32 or rec.shape[1] < need \
+            or rec.stride(1) != 1 or out.stride(1) != 1 or not state.is_contiguous() or state.shape[1] < heads * head_dim * v_dim:
+        raise KernelError("linear_scan: float32 operands of the sizes the heads need")
+    if not gated and (decay is None or decay.dtype != torch.float32 or decay.numel() != heads):
+        raise KernelError("linear_scan: one float32 decay per head")
+    base = rec.data_ptr()
+    g_ptr = base + 4 * (off_v + heads * v_dim) if gated else None
+    b_ptr = base + 4 * (off_v + heads * v_dim + heads) if gated else None
+    lib.call("ns_linear_scan", base, base + 4 * kv_heads * dp, base + 4 * off_v, g_ptr, b_ptr, None if gated else decay.data_ptr(),
+             rec.stride(0), state.data_ptr(), state.stride(0), ctx.qo_indptr.data_ptr(), ctx.state_slot.data_ptr(), out.data_ptr(),
+             out.stride(0), ctx.n_requests, heads, kv_heads, head_dim, v_dim, _stream())
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor | None, gain: torch.Tensor | None, eps: float, out: torch.Tensor, ctx,
+                   heads: int, v_dim: int) -> torch.Tensor:
+    """out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * gain * silu(gate[n, h, :]); `gate` may be a column range of
+    a packed projection, `gain` [v_dim] float32 or None."""
+    _cuda(o, gate, gain, out)
+    if o.dtype != torch.float32 or o.stride(1) != 1 or out.stride(1) != 1 or (gate is not None and (gate.stride(1) != 1 or gate.dtype != out.dtype)):
+        raise KernelError("head_norm_gate: a float32 read-out, row-major operands, the gate in the output's dtype")
+    lib.call("ns_head_norm_gate", o.data_ptr(), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(gain), float(eps),
+             out.data_ptr(), out.stride(0), ctx.token_req.data_ptr(), o.shape[0], heads, v_dim, dtype_code(out.dtype), _stream())
+    return out

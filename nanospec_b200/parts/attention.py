@@ -27,7 +27,13 @@ from .registry import build_part, register_part
 @register_part("mixer", "gqa_attention")
 class GQAAttention(Part):
     """params: hidden, heads, kv_heads, head_dim, window (0 = all keys), position (PartSpec),
-    scale (optional; default 1/sqrt(head_dim))."""
+    scale (optional; default 1/sqrt(head_dim)); and, all optional:
+    v_dim        the values' head size when it is not the keys' (the output projection then takes heads * v_dim)
+    keep_first   with a window: the first so many keys of a sequence stay visible to every later query
+    qk_norm      {"eps": e}: an RMS norm over the whole q projection and one over the whole k projection (one statistic
+                 over all heads, gains `q_norm` / `k_norm` of the projections' sizes), before the rotation
+    names        the tensors' names after the part's prefix, keys "q", "k", "v", "o", "q_norm", "k_norm"
+                 (default the Hugging Face ones)."""
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
@@ -40,27 +46,48 @@ class GQAAttention(Part):
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads cannot be shared among {self.kv_heads} kv heads")
+        self.v_dim = int(p.get("v_dim") or self.head_dim)
+        self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
+        self.qk_norm = dict(p["qk_norm"]) if p.get("qk_norm") else None
+        names = dict(p.get("names") or {})
+        self.names = {k: names.get(k, d) for k, d in (("q", "q_proj.weight"), ("k", "k_proj.weight"), ("v", "v_proj.weight"),
+                                                      ("o", "o_proj.weight"), ("q_norm", "q_norm.weight"), ("k_norm", "k_norm.weight"))}
         self.q_size = self.heads * self.head_dim
         self.kv_size = self.kv_heads * self.head_dim
+        self.v_size = self.kv_heads * self.v_dim
+        self.o_in = self.heads * self.v_dim
+        # what the llama-shaped fast paths (a projection with the rotation in its epilogue) do not know of
+        self.general = self.v_dim != self.head_dim or self.qk_norm is not None
+        self.q_gain: torch.Tensor | None = None
+        self.k_gain: torch.Tensor | None = None
         self.position = build_part("position", p["position"], dtype, device) if p.get("position") is not None else None
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
 
     def weight_specs(self) -> dict[str, WeightSpec]:
-        return {
-            "q_proj.weight": WeightSpec((self.q_size, self.hidden)),
-            "k_proj.weight": WeightSpec((self.kv_size, self.hidden)),
-            "v_proj.weight": WeightSpec((self.kv_size, self.hidden)),
-            "o_proj.weight": WeightSpec((self.hidden, self.q_size)),
+        n = self.names
+        specs = {
+            n["q"]: WeightSpec((self.q_size, self.hidden)),
+            n["k"]: WeightSpec((self.kv_size, self.hidden)),
+            n["v"]: WeightSpec((self.v_size, self.hidden)),
+            n["o"]: WeightSpec((self.hidden, self.o_in)),
         }
+        if self.qk_norm is not None:
+            specs[n["q_norm"]] = WeightSpec((self.q_size,), rule="float32", init="gain")
+            specs[n["k_norm"]] = WeightSpec((self.kv_size,), rule="float32", init="gain")
+        return specs
 
     def bind(self, tensors) -> None:
+        n = self.names
         # one packed projection [q | k | v]: one matrix product instead of three
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        self.w_qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        if self.qk_norm is not None:
+            self.q_gain, self.k_gain = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
 
     def cache_need(self) -> CacheNeed | None:
-        return CacheNeed(self.kv_heads, self.head_dim, self.window)
+        return CacheNeed(self.kv_heads, self.head_dim, self.window, self.keep_first,
+                         None if self.v_dim == self.head_dim else self.v_dim)
 
     def state_need(self) -> StateNeed | None:
         return None
@@ -72,7 +99,18 @@ class GQAAttention(Part):
         return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_o)
 
     def forward(self, x, ctx: StepContext, lane: LaneView, writes: bool = True, sink: ops.NormSink | None = None):
-        qkv = ctx.buffer("qkv", self.q_size + 2 * self.kv_size)
+        qkv = ctx.buffer("qkv", self.q_size + self.kv_size + self.v_size)
+        if self.general:
+            ops.linear(x, self.w_qkv, qkv)
+            if self.position is None:
+                raise ValueError("an attention mixer with qk_norm or v_dim takes a position part with the general rotate_and_store")
+            qn = self.qk_norm
+            self.position.rotate_and_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes, v_dim=self.v_dim,
+                                           q_gain=self.q_gain, k_gain=self.k_gain, eps=float(qn["eps"]) if qn else 0.0)
+            attn = ctx.buffer("attn_out", self.o_in)
+            ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window,
+                          self.keep_first, self.v_dim)
+            return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)
         fused = getattr(self.position, "project_rotate_store", None)
         if fused is None or not fused(x, self.w_qkv, qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes):
             ops.linear(x, self.w_qkv, qkv)
@@ -81,5 +119,5 @@ class GQAAttention(Part):
             elif writes:
                 ops.kv_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim)
         attn = ctx.buffer("attn_out", self.q_size)
-        ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window)
+        ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window, self.keep_first)
         return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)

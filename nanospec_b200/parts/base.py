@@ -58,12 +58,15 @@ class Part:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Paged key/value storage a mixer wants: per token `kv_heads * head_dim` keys and as many
-    values; `window` > 0 means only the last `window` positions are ever read."""
+    """Paged key/value storage a mixer wants: per token `kv_heads * head_dim` keys and `kv_heads * v_dim`
+    values (`v_dim` None: as wide as the keys); `window` > 0 means only the last `window` positions are ever
+    read, and beside them the first `keep_first` positions of the sequence."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    keep_first: int = 0
+    v_dim: int | None = None
 
 
 @dataclass(frozen=True)

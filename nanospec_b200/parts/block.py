@@ -30,6 +30,11 @@ from .context import LaneView, StepContext
 from .registry import build_part, register_part
 
 
+def _folds(norm) -> bool:
+    """Whether a norm can be folded into the products around it (it offers `sink`)."""
+    return callable(getattr(norm, "sink", None))
+
+
 def _can(part, what: str, n_tokens: int) -> bool:
     """A part's optional capability (`takes_row_scaled`, `feeds_norm_sink`); parts that do not know of it have none."""
     f = getattr(part, what, None)
@@ -44,16 +49,17 @@ class PreNormBlock:
     def __init__(self, layer: LayerSpec, dtype: torch.dtype, device: torch.device) -> None:
         self.layer = layer
         self.mixer = build_part("mixer", layer.mixer, dtype, device)
-        self.feed_forward = build_part("feed_forward", layer.feed_forward, dtype, device)
         self.norm_mixer = build_part("norm", layer.norm, dtype, device)
-        self.norm_feed_forward = build_part("norm", layer.norm, dtype, device)
+        # a layer without a feed-forward (`LayerSpec.feed_forward` None) is its first sublayer alone
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, dtype, device) if layer.feed_forward is not None else None
+        self.norm_feed_forward = build_part("norm", layer.norm, dtype, device) if layer.feed_forward is not None else None
 
     def parts(self) -> dict:
-        return {s: getattr(self, s) for s in self.slots}
+        return {s: getattr(self, s) for s in self.slots if getattr(self, s) is not None}
 
     def input_norm_sink(self, resid: torch.Tensor, ctx: StepContext):
         """What the product before this block needs to fold the block's first norm in, or None."""
-        if _can(self.mixer, "takes_row_scaled", ctx.n_tokens) and hasattr(self.norm_mixer, "sink"):
+        if _can(self.mixer, "takes_row_scaled", ctx.n_tokens) and _folds(self.norm_mixer):
             return self.norm_mixer.sink(resid, ctx)
         return None
 
@@ -61,8 +67,15 @@ class PreNormBlock:
                 follow=None) -> tuple[torch.Tensor, torch.Tensor]:
         n = ctx.n_tokens
         x = self.norm_mixer.add_norm(resid, pending, ctx)
+        if self.feed_forward is None:
+            sink = None
+            if follow is not None and _can(self.mixer, "feeds_norm_sink", n) and hasattr(follow, "input_norm_sink"):
+                sink = follow.input_norm_sink(resid, ctx)
+            if sink is not None:
+                return resid, self.mixer.forward(x, ctx, lane, writes, sink=sink)
+            return resid, self.mixer.forward(x, ctx, lane, writes)
         if _can(self.mixer, "feeds_norm_sink", n) and _can(self.feed_forward, "takes_row_scaled", n) \
-                and hasattr(self.norm_feed_forward, "sink"):
+                and _folds(self.norm_feed_forward):
             a = self.mixer.forward(x, ctx, lane, writes, sink=self.norm_feed_forward.sink(resid, ctx))
         else:
             a = self.mixer.forward(x, ctx, lane, writes)

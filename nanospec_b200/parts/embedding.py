@@ -14,18 +14,19 @@ from .registry import register_part
 
 @register_part("embedding", "table")
 class TokenEmbedding(Part):
-    """params: vocab, hidden."""
+    """params: vocab, hidden, weight_name (the table's name after the part's prefix; default "weight")."""
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
+        self.weight_name = spec.params.get("weight_name", "weight")
         self.table: torch.Tensor | None = None
 
     def weight_specs(self) -> dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.vocab, self.hidden))}
+        return {self.weight_name: WeightSpec((self.vocab, self.hidden))}
 
     def bind(self, tensors) -> None:
-        self.table = tensors["weight"].contiguous()
+        self.table = tensors[self.weight_name].contiguous()
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         return ops.embed(self.table, ctx.token_ids, ctx.buffer("resid", self.hidden, torch.float32))
@@ -33,22 +34,30 @@ class TokenEmbedding(Part):
 
 @register_part("head", "linear")
 class LinearHead(Part):
-    """params: vocab, hidden, tied_to (full name of the embedding table, or None)."""
+    """params: vocab, hidden, tied_to (full name of the embedding table, or None), weight_name (default "weight"),
+    scale (the logits are multiplied by it; default 1) and softcap (c > 0: logits = c * tanh(logits / c), after the
+    scale; default none)."""
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
         self.tied_to = spec.params.get("tied_to")
+        self.weight_name = spec.params.get("weight_name", "weight")
+        self.scale = float(spec.params.get("scale") or 1.0)
+        self.softcap = float(spec.params.get("softcap") or 0.0)
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.vocab, self.hidden), alias=self.tied_to)}
+        return {self.weight_name: WeightSpec((self.vocab, self.hidden), alias=self.tied_to)}
 
     def bind(self, tensors) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
 
     def forward(self, h: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """h [R, hidden] compute dtype -> float32 logits [R, vocab]."""
         if out is None:
             out = torch.empty((h.shape[0], self.vocab), dtype=torch.float32, device=h.device)
-        return ops.linear(h, self.weight, out)
+        ops.linear(h, self.weight, out)
+        if self.scale != 1.0 or self.softcap > 0.0:
+            ops.scale_softcap(out, self.scale, self.softcap)
+        return out

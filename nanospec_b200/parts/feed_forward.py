@@ -20,25 +20,30 @@ from .registry import register_part
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
-    """params: hidden, intermediate."""
+    """params: hidden, intermediate, names (optional: the tensors' names after the part's prefix, keys "gate", "up",
+    "down"; default the Hugging Face ones)."""
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
         self.hidden = int(spec["hidden"])
         self.inter = int(spec["intermediate"])
+        names = dict(spec.params.get("names") or {})
+        self.n_gate = names.get("gate", "gate_proj.weight")
+        self.n_up = names.get("up", "up_proj.weight")
+        self.n_down = names.get("down", "down_proj.weight")
         self.w_gate_up: torch.Tensor | None = None
         self.w_down: torch.Tensor | None = None
         self.gate_block = 0
 
     def weight_specs(self) -> dict[str, WeightSpec]:
         return {
-            "gate_proj.weight": WeightSpec((self.inter, self.hidden)),
-            "up_proj.weight": WeightSpec((self.inter, self.hidden)),
-            "down_proj.weight": WeightSpec((self.hidden, self.inter)),
+            self.n_gate: WeightSpec((self.inter, self.hidden)),
+            self.n_up: WeightSpec((self.inter, self.hidden)),
+            self.n_down: WeightSpec((self.hidden, self.inter)),
         }
 
     def bind(self, tensors) -> None:
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        gate, up = tensors[self.n_gate], tensors[self.n_up]
         self.gate_block = ops.GATE_BLOCK if self.inter % ops.GATE_BLOCK == 0 else 0
         if self.gate_block:
             b = self.gate_block
@@ -46,7 +51,7 @@ class SwiGLU(Part):
             self.w_gate_up = packed.reshape(2 * self.inter, self.hidden).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_down = tensors[self.n_down].contiguous()
 
     def takes_row_scaled(self, n_tokens: int) -> bool:
         return ops.norm_fusion_ok(n_tokens, self.dtype, self.w_gate_up)

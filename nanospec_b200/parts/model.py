@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import ops
 from ..config.recipe import ModelRecipe
 from .base import CacheNeed, StateNeed, WeightSpec
 from .context import StepContext
@@ -31,12 +32,13 @@ class DecoderModel:
     # ---- weights ---------------------------------------------------------------------
     def _named_parts(self):
         r = self.recipe
-        yield r.embedding.params.get("name", "model.embed_tokens") + ".", self.embedding
+        # an embedding or head whose spec gives "prefix" names its tensors under that instead of `name` + "."
+        yield r.embedding.params.get("prefix", r.embedding.params.get("name", "model.embed_tokens") + "."), self.embedding
         for layer, block in zip(r.layers, self.blocks):
             for slot, part in block.parts().items():
                 yield layer.prefix + layer.names[slot], part
         yield r.final_norm_prefix, self.final_norm
-        yield r.head.params.get("name", "lm_head") + ".", self.head
+        yield r.head.params.get("prefix", r.head.params.get("name", "lm_head") + "."), self.head
 
     def weight_specs(self) -> dict[str, WeightSpec]:
         """Full checkpoint name -> what is wanted under it."""
@@ -69,14 +71,29 @@ class DecoderModel:
         resid = self.embedding.forward(ctx)
         pending = None
         order = self.recipe.order
+        first = None
+        if any(run.add_input for run in order):
+            # the stream as the embedding leaves it, for the runs that add it again (float32, like the stream)
+            first = ctx.buffer("resid_input", self.hidden_size, torch.float32)
+            first.copy_(resid)
         for i, run in enumerate(order):
+            if run.add_input:
+                if pending is not None:
+                    if isinstance(pending, ops.RowScaled):
+                        raise RuntimeError("a branch folded into a norm cannot precede a run that adds the input")
+                    ops.residual_add(resid, pending)
+                    pending = None
+                ops.residual_add(resid, first)
             # the block that runs next: its first norm may be folded into this block's last product
-            follow = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            follow = self.blocks[order[i + 1].layer] if i + 1 < len(order) and not order[i + 1].add_input else None
             block = self.blocks[run.layer]
             if follow is not None and getattr(block, "takes_follow", False):
                 resid, pending = block.forward(resid, pending, ctx, ctx.lanes[run.lane], run.writes, follow=follow)
             else:
                 resid, pending = block.forward(resid, pending, ctx, ctx.lanes[run.lane], run.writes)
+            probe = ctx.extras.get("probe")
+            if probe is not None:  # a debugging hook: probe(run index, stream, branch not yet added to it)
+                probe(i, resid, pending)
         if want_rows is None and not all_rows:
             return None
         return self.final_norm.add_norm(resid, pending, ctx, rows=want_rows, out_name="final_normed")

@@ -1,4 +1,4 @@
-"""RMSNorm over the float32 residual stream, fused with the residual sum.
+"""Norms over the float32 residual stream, fused with the residual sum: RMSNorm and a layer norm without bias.
 
 Formula of the reference (model/llama.py:86-95): h = x * rsqrt(mean(x^2) + eps), y = gain * h,
 eps inside the root, the gain applied as is (not 1 + gain).  Here the statistics, the scale
@@ -28,17 +28,20 @@ from .registry import register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
+    """params: hidden, eps, weight_name (the gain's name after the norm's prefix; default "weight")."""
+
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
         self.hidden = int(spec["hidden"])
         self.eps = float(spec["eps"])
+        self.weight_name = spec.params.get("weight_name", "weight")
         self.gain: torch.Tensor | None = None
 
     def weight_specs(self) -> dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.hidden,), rule="float32", init="gain")}
+        return {self.weight_name: WeightSpec((self.hidden,), rule="float32", init="gain")}
 
     def bind(self, tensors) -> None:
-        self.gain = tensors["weight"].contiguous()
+        self.gain = tensors[self.weight_name].contiguous()
 
     def sink(self, resid: torch.Tensor, ctx: StepContext) -> ops.NormSink:
         return ops.NormSink(resid, self.gain, self.eps, ctx.workspace)
@@ -53,3 +56,20 @@ class RMSNorm(Part):
         n = resid.shape[0] if rows is None else rows.numel()
         out = ctx.buffer(out_name, self.hidden, rows=n)
         return ops.add_rmsnorm(resid, pending, self.gain, self.eps, out, rows=rows)
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(RMSNorm):
+    """(x - mean) / sqrt(var + eps) * gain: the variance is the mean of the squared deviations, there is no bias.
+    Mean and variance are taken in float32 in two passes over the row.  It has no `sink`: a centred norm is not a
+    per-row scale of the stream, so it is never folded into the products around it.  params as `rmsnorm`."""
+
+    sink = None  # hasattr(norm, "sink") is what the blocks ask; None says it cannot be folded
+
+    def add_norm(self, resid: torch.Tensor, pending, ctx: StepContext,
+                 rows: torch.Tensor | None = None, out_name: str = "normed"):
+        if isinstance(pending, ops.RowScaled):
+            raise ValueError("a RowScaled reached a norm that cannot take it")
+        n = resid.shape[0] if rows is None else rows.numel()
+        out = ctx.buffer(out_name, self.hidden, rows=n)
+        return ops.add_layernorm(resid, pending, self.gain, self.eps, out, rows=rows)

@@ -71,3 +71,62 @@ class RotaryEncoding(Part):
                              nkv: int, head_dim: int, writes: bool) -> bool:
         return ops.linear_rope(x, w_qkv, qkv, ctx.positions, ctx.token_req, lane.block_table, self.inv_freq, lane.k, lane.v,
                                lane.page_size, nq, nkv, head_dim, write_kv=writes)
+
+
+def rotary_frequencies(dims: int, base: float, scaling: dict | None) -> tuple[torch.Tensor, float]:
+    """Frequencies of the dims / 2 rotated pairs (float32 on the CPU) and the factor on cos and sin.
+
+    Without scaling f_i = base^(-2i / dims).  With the YaRN block (`factor`, `original`, `fast`, `slow`): a pair
+    that makes `t` turns over `original` positions sits at d(t) = dims * ln(original / (2 pi t)) / (2 ln base);
+    pairs up to floor(d(fast)) keep f_i, pairs from ceil(d(slow)) on turn `factor` times slower, and a linear
+    ramp joins them; cos and sin are multiplied by 0.1 * ln(factor) + 1.
+    """
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    if not scaling:
+        return f.to(torch.float32), 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def at(turns: float) -> float:
+        return dims * math.log(original / (2 * math.pi * turns)) / (2 * math.log(float(base)))
+
+    lo = max(math.floor(at(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(at(float(scaling["slow"]))), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32), 0.1 * math.log(factor) + 1.0
+
+
+@register_part("position", "rotary")
+class Rotary(Part):
+    """Rotation of the first `dims` features of every q and k head, in either pairing.
+
+    params: head_dim, dims (how many features turn, even, at most head_dim), base, layout ("half": pairs
+    (i, i + dims/2); "interleaved": pairs (2i, 2i + 1)), scaling (None or the YaRN block, see `rotary_frequencies`).
+    An attention mixer calls `rotate_and_store` (which can also norm the whole q and k projections first and takes
+    values of another width than the keys); a mixer with a state reads `inv_freq`, `magnitude` and `interleaved`.
+    """
+
+    def __init__(self, spec, dtype, device) -> None:
+        super().__init__(spec, dtype, device)
+        self.head_dim = int(spec["head_dim"])
+        self.dims = int(spec.params.get("dims", self.head_dim))
+        layout = spec.params.get("layout", "half")
+        if layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary: unknown layout {layout!r}")
+        if self.dims % 2 or not 0 <= self.dims <= self.head_dim:
+            raise ValueError(f"rotary: {self.dims} of {self.head_dim} features cannot be rotated in pairs")
+        self.interleaved = layout == "interleaved"
+        scaling = spec.params.get("scaling")
+        self.inv_freq_host, self.magnitude = rotary_frequencies(self.dims, float(spec["base"]), dict(scaling) if scaling else None)
+        self._inv_freq: torch.Tensor | None = None
+
+    @property
+    def inv_freq(self) -> torch.Tensor:
+        if self._inv_freq is None:
+            self._inv_freq = self.inv_freq_host.to(self.device).contiguous()
+        return self._inv_freq
+
+    def rotate_and_store(self, qkv: torch.Tensor, ctx: StepContext, lane: LaneView, nq: int, nkv: int, head_dim: int,
+                         writes: bool, v_dim: int | None = None, q_gain=None, k_gain=None, eps: float = 0.0) -> None:
+        ops.qk_norm_rope_store(qkv, ctx, lane, self.inv_freq if self.dims else None, self.magnitude, self.interleaved, nq, nkv,
+                               head_dim, head_dim if v_dim is None else v_dim, q_gain, k_gain, eps, write_kv=writes)
