@@ -176,5 +176,5 @@ def forward(cfg: dict, w: dict, tokens: list[int], dtype=torch.float64, trace: l
         if trace is not None:
             trace.append(x.clone())
     logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T * float(cfg["logit_scale"])
-    cap = float(cfg["logit_softcap"])
-    return cap * torch.tanh(logits / cap)
+    cap = float(cfg.get("logit_softcap") or 0.0)
+    return cap * torch.tanh(logits / cap) if cap > 0 else logits
