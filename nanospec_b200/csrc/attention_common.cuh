@@ -13,10 +13,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 // Rows key0 .. key0+63 of one kv head: cache[page, hk, offset, :] with page = bt[key / page_size].
 // Rows before key_lo (their pages may already have been given back behind a window) and rows at or
 // beyond key_end are not read but zero-filled (a masked weight of zero must not meet a NaN).
+// Kept first keys behind a window: the caller counts keys in a virtual range in which the kept keys lie
+// directly before the window; a virtual key below key_split is the real key (virtual - gap).  With
+// gap == 0 virtual and real keys are the same.
 template <int D, int THREADS = kThreads>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs, const __nv_bfloat16* k_cache,
                                              const __nv_bfloat16* v_cache, const int* bt, int key0, int key_lo, int key_end,
-                                             int hk, int nkv, int page_size, int page_shift) {
+                                             int hk, int nkv, int page_size, int page_shift, int key_split = 0, int gap = 0) {
     constexpr int kChunks = D / 8;
     constexpr int kItems = (kTileKeys * kChunks + THREADS - 1) / THREADS;  // 16-byte pieces per thread and tensor
     // When the threads divide evenly over the pieces of a row, a thread keeps the same piece of
@@ -33,8 +36,9 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
     for (int i = 0; i < kItems; ++i) {
         const int c = threadIdx.x + i * THREADS;
         const int row = kRegular ? row0 + i * kRowStep : c / kChunks;
-        const int key = key0 + row;
-        const bool valid = c < kTileKeys * kChunks && key >= key_lo && key < key_end;
+        const int vkey = key0 + row;
+        const int key = vkey >= key_split ? vkey : vkey - gap;
+        const bool valid = c < kTileKeys * kChunks && vkey >= key_lo && vkey < key_end;
         // page_shift >= 0: the page size is a power of two (no integer division per row)
         page[i] = valid ? __ldg(bt + (page_shift >= 0 ? key >> page_shift : key / page_size)) : -1;
     }
@@ -44,7 +48,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
         if (c >= kTileKeys * kChunks) break;
         const int row = kRegular ? row0 + i * kRowStep : c / kChunks;
         const int ch = kRegular ? ch0 : c - row * kChunks;
-        const int key = key0 + row;
+        const int vkey = key0 + row;
+        const int key = vkey >= key_split ? vkey : vkey - gap;
         const bool valid = page[i] >= 0;
         size_t off = 0;
         if (valid) {

@@ -30,7 +30,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ qo_indptr, __nv_bfloat16* __restrict__ out, int o_stride,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                         const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
-                        int n_splits, int head_tiles) {
+                        int n_splits, int head_tiles, int keep_first) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -51,7 +51,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int gcount = min(16, G - ht * 16);
     const int pos = positions[n];
     const int kend = pos + 1;
-    const int kstart = (window > 0 && kend - window > 0) ? kend - window : 0;
+    // With kept first keys behind a window the block counts keys in a virtual range [kstart, kend) in which the kept keys
+    // lie directly before the window: a virtual key below win_start is the real key (virtual - gap); see load_kv_tile.
+    const int win_start = (window > 0 && kend - window > 0) ? kend - window : 0;
+    const int gap = win_start - min(keep_first, win_start);
+    const int kstart = gap;
     const int chunk = (((kend - kstart + n_splits - 1) / n_splits + kTileKeys - 1) / kTileKeys) * kTileKeys;
     const int k0 = kstart + split * chunk;
     const int k1 = min(k0 + chunk, kend);
@@ -75,7 +79,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     for (int st = 0; st < kStages - 1; ++st) {
         if (st < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)st * 2 * kTileKeys * S;
-            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size, page_shift);
+            load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + st * kTileKeys, kstart, k1, hk, nkv, page_size, page_shift, win_start, gap);
         }
         ns_cp_async_commit();
     }
@@ -97,7 +101,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         if (t + kStages - 1 < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)((t + kStages - 1) % kStages) * 2 * kTileKeys * S;
             load_kv_tile<D>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k0 + (t + kStages - 1) * kTileKeys, kstart, k1, hk,
-                            nkv, page_size, page_shift);
+                            nkv, page_size, page_shift, win_start, gap);
         }
         ns_cp_async_commit();
         ns_cp_async_wait<kStages - 1>();  // tile t has landed; the two after it stay in flight
@@ -264,7 +268,7 @@ template <int D, int kStages>
 int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0) {
     constexpr int S = NsTile<D>::kStride;
     const size_t tiles = (size_t)(16 + 2 * kStages * kTileKeys) * S * sizeof(__nv_bfloat16);
     const size_t scratch = (size_t)(4 * 16 * D + 128) * sizeof(float);  // the warps' partial results reuse the k/v stages
@@ -279,7 +283,7 @@ int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const
     NS_LAUNCH((attention_decode_kernel<D, kStages>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
-        nkv, page_size, scale, window, n_splits, head_tiles);
+        nkv, page_size, scale, window, n_splits, head_tiles, keep_first);
     NS_CHECK_LAUNCH("ns_attention_decode");
     return NS_OK;
 }
@@ -290,14 +294,14 @@ template <int D>
 int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0) {
     if (g_decode_stages == 2)
         return launch_decode_stages<D, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                           qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                          page_size, scale, window, n_splits, stream);
+                                          page_size, scale, window, n_splits, stream, keep_first);
     return launch_decode_stages<D, 3>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                       qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                      page_size, scale, window, n_splits, stream);
+                                      page_size, scale, window, n_splits, stream, keep_first);
 }
 
 }  // namespace
@@ -322,12 +326,15 @@ NS_API int ns_attention_decode_scratch(int n_tokens, int nq, int nkv, int d, int
 // bfloat16 only; head_dim a multiple of 16 up to 128.  `counters` must be zero before the first
 // launch; every launch leaves it zero again.  `rows` (optional) lists the token rows to work on
 // (n_tokens of them); without it the tokens are 0 .. n_tokens-1.
-NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
-                               const int* block_table, int table_stride, const int* token_req, const int* positions,
-                               const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
-                               int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
-                               float scale, int window, int n_splits, cudaStream_t stream) {
+// `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
+NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                    const int* block_table, int table_stride, const int* token_req, const int* positions,
+                                    const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
+                                    int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
+                                    float scale, int window, int keep_first, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
+    if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: window=%d keep_first=%d", window, keep_first);
+    if (window == 0) keep_first = 0;
     if (d % 16 || d < 16 || d > 128)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d (multiples of 16 up to 128)", d);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: %d query heads over %d kv heads", nq, nkv);
@@ -338,13 +345,23 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
     case DD:                                                                                                           \
         return launch_decode<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,       \
                                  qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,         \
-                                 page_size, scale, window, n_splits, stream);
+                                 page_size, scale, window, n_splits, stream, keep_first);
     switch (d) {
         NS_DECODE_CASE(16) NS_DECODE_CASE(32) NS_DECODE_CASE(48) NS_DECODE_CASE(64)
         NS_DECODE_CASE(80) NS_DECODE_CASE(96) NS_DECODE_CASE(112) NS_DECODE_CASE(128)
     }
 #undef NS_DECODE_CASE
     NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_decode: head_dim=%d", d);
+}
+
+NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                               const int* block_table, int table_stride, const int* token_req, const int* positions,
+                               const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
+                               int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
+                               float scale, int window, int n_splits, cudaStream_t stream) {
+    return ns_attention_decode_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr, out,
+                                    o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, d, page_size, scale, window, 0,
+                                    n_splits, stream);
 }
 
 // ---------------------------------------------------------------------------------------

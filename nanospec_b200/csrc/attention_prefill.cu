@@ -7,7 +7,9 @@
 // owns 16 query rows.  Keys and values of the head's kv head stream through shared memory with
 // cp.async in tiles of 64 (two stages); scores and the weighted sum run on the tensor cores
 // (m16n8k16), the softmax is online in fp32 (base 2).  A query at position p sees keys
-// max(0, p - window + 1) .. p (window 0: all of 0 .. p).
+// max(0, p - window + 1) .. p (window 0: all of 0 .. p) and, with keep_first > 0, the keys 0 .. keep_first - 1 as
+// well: the block then counts keys in a virtual range in which the kept keys lie directly before the first row's
+// window (see load_kv_tile) and masks by the real key.
 //
 // Requests that bring exactly one token are left to the decode kernel; the host lists no tile
 // for them.
@@ -24,7 +26,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
-                         int page_size, float scale, int window) {
+                         int page_size, float scale, int window, int keep_first) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -41,8 +43,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     const int pos0 = positions[tok0];                         // positions of a request's tokens are consecutive
     const int pos_last = pos0 + rows - 1;
     const int kend = pos_last + 1;
-    const int kfirst = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int k_begin = (kfirst / kTileKeys) * kTileKeys;
+    const int win_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;  // first key of the first row's window
+    const int gap = win_first - min(keep_first, win_first);  // real keys that the virtual range leaves out before the window
+    const int kfirst = gap;                                   // first virtual key
+    const int k_begin = gap < win_first ? kfirst : (kfirst / kTileKeys) * kTileKeys;
     const int n_tiles = (kend - k_begin + kTileKeys - 1) / kTileKeys;
     const int* bt = block_table + (size_t)req * table_stride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -57,7 +61,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             ns_cp_async16(Tile::at(qs, row, ch * 8), qbase + (valid ? (size_t)row * q_stride + ch * 8 : 0), valid);
         }
     }
-    load_kv_tile<D, kPrefillThreads>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k_begin, kfirst, kend, hk, nkv, page_size, page_shift);
+    load_kv_tile<D, kPrefillThreads>(kv, kv + kTileKeys * S, k_cache, v_cache, bt, k_begin, kfirst, kend, hk, nkv, page_size, page_shift, win_first, gap);
     ns_cp_async_commit();
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -82,7 +86,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
         if (t + 1 < n_tiles) {
             __nv_bfloat16* kn = kv + (size_t)((t + 1) & 1) * 2 * kTileKeys * S;
             load_kv_tile<D, kPrefillThreads>(kn, kn + kTileKeys * S, k_cache, v_cache, bt, k_begin + (t + 1) * kTileKeys, kfirst, kend, hk,
-                            nkv, page_size, page_shift);
+                            nkv, page_size, page_shift, win_first, gap);
         }
         ns_cp_async_commit();
         ns_cp_async_wait<1>();
@@ -112,7 +116,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             float mx[2] = {-INFINITY, -INFINITY};
             // tiles that lie wholly inside every row's visible range need no mask
             const int warp_pos_min = pos0 + min(warp * 16, rows - 1);
-            const bool full = kb + kTileKeys - 1 <= warp_pos_min && (window <= 0 || kb > warp_pos_max - window);
+            const bool full = kb + kTileKeys - 1 <= warp_pos_min && (window <= 0 || kb > warp_pos_max - window) && kb >= win_first;
             if (full) {
 #pragma unroll
                 for (int nb = 0; nb < 8; ++nb)
@@ -127,9 +131,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const int key = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
+                        const int vkey = kb + nb * 8 + 2 * (lane & 3) + (j & 1);
+                        const int key = vkey >= win_first ? vkey : vkey - gap;
                         const int p = prow[j >> 1];
-                        const bool seen = key <= p && (window <= 0 || key > p - window);
+                        const bool seen = key <= p && (window <= 0 || key > p - window || key < keep_first) && vkey >= kfirst;
                         const float v = seen ? s[nb][j] * sl : -INFINITY;
                         s[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
@@ -202,7 +207,7 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                    int table_stride, const int* positions, const int* qo_indptr, const int* tiles, int n_tiles,
                    void* out, int o_stride, int nq, int nkv, int page_size, float scale, int window,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, int keep_first = 0) {
     constexpr int S = NsTile<D>::kStride;
     const size_t smem = (size_t)(kTileQ + 4 * kTileKeys) * S * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -213,7 +218,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
     dim3 grid(n_tiles, nq);
     NS_LAUNCH((attention_prefill_kernel<D>), grid, kPrefillThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
-        table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window);
+        table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first);
     NS_CHECK_LAUNCH("ns_attention_prefill");
     return NS_OK;
 }
@@ -222,11 +227,14 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
 
 // tiles: int32 [n_tiles, 2] = (request, offset of the tile's first token among the request's
 // tokens of this step, a multiple of 128).  bfloat16 only; head_dim a multiple of 16 up to 128.
-NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,
-                                const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
-                                const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
-                                int page_size, float scale, int window, cudaStream_t stream) {
+// `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
+NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                     const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
+                                     const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
+                                     int page_size, float scale, int window, int keep_first, cudaStream_t stream) {
     if (n_tiles <= 0) return NS_OK;
+    if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill: window=%d keep_first=%d", window, keep_first);
+    if (window == 0) keep_first = 0;
     if (d % 16 || d < 16 || d > 128)
         NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: head_dim=%d (multiples of 16 up to 128)", d);
     if (nkv < 1 || nq % nkv) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: %d query heads over %d kv heads", nq, nkv);
@@ -236,11 +244,19 @@ NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache
 #define NS_PREFILL_CASE(DD)                                                                                          \
     case DD:                                                                                                         \
         return launch_prefill<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr,   \
-                                  tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream);
+                                  tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first);
     switch (d) {
         NS_PREFILL_CASE(16) NS_PREFILL_CASE(32) NS_PREFILL_CASE(48) NS_PREFILL_CASE(64)
         NS_PREFILL_CASE(80) NS_PREFILL_CASE(96) NS_PREFILL_CASE(112) NS_PREFILL_CASE(128)
     }
 #undef NS_PREFILL_CASE
     NS_FAIL(NS_ERR_UNSUPPORTED, "ns_attention_prefill: head_dim=%d", d);
+}
+
+NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
+                                const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
+                                int page_size, float scale, int window, cudaStream_t stream) {
+    return ns_attention_prefill_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr, tiles, n_tiles,
+                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, stream);
 }

@@ -526,7 +526,7 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
 
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                      window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None,
-                     work: torch.Tensor | None = None, work_slots: int = 0) -> None:
+                     work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0) -> None:
     """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
     pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
     (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
@@ -536,7 +536,11 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
     a window: a request whose context is much longer than the others' comes as several items, a part of its keys
     each, and the kernel adds the parts up through `work_slots` slots of scratch."""
     head_tiles = -(-(nq // nkv) // 16)
-    if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0:
+    if window == 0:
+        keep_first = 0
+    # (kept first keys behind a window are the cp.async kernel's: the TMA kernel loads whole pages in key order)
+    if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0 \
+            and not keep_first:
         n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
         if work is not None and window == 0:
             ws = ctx.workspace
@@ -560,22 +564,24 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
         # and a split keeps at least two tiles of keys
         n_splits = max(n_splits, min(4, max_kv_len // 1024))
         n_splits = max(1, min(n_splits, -(-max_kv_len // 128)))
+        if window > 0:  # ... of the keys that are visible
+            n_splits = max(1, min(n_splits, -(-min(max_kv_len, window + keep_first) // 128)))
     ws = ctx.workspace
     part_o = ws.get("attn_part_o", n_rows * nq * n_splits, head_dim, torch.float32)
     part_ml = ws.get("attn_part_ml", n_rows * nq * n_splits, 2, torch.float32)
     counters = ws.get("attn_counters", n_rows * nkv * head_tiles, 1, torch.int32, zero=True)
-    lib.call("ns_attention_decode", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+    lib.call("ns_attention_decode_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
              ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
              counters.data_ptr(), _ptr(rows), n_rows, nq, nkv, head_dim, lane.page_size, float(scale), int(window),
-             n_splits, _stream())
+             int(keep_first), n_splits, _stream())
 
 
 PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whatever the size of the grid
 
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-                      window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None) -> None:
+                      window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None, keep_first: int = 0) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
     among its tokens of this step).  Head sizes 64 and 128 with pages of 8 to 64 tokens and no window run
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
@@ -591,10 +597,10 @@ def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, 
                  out.stride(0), nq, nkv, head_dim, lane.page_size, float(scale), 2 if two_heads else 1,
                  _tc(qkv.device).error.data_ptr(), _stream())
         return
-    lib.call("ns_attention_prefill", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
+    lib.call("ns_attention_prefill_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
              tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,
-             float(scale), int(window), _stream())
+             float(scale), int(window), int(keep_first) if window else 0, _stream())
 
 
 def _attention_plan(ctx) -> dict:
@@ -637,8 +643,9 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
     that bring one token, the prefill kernel for the others.  float32, and head sizes those
     kernels refuse: the exact kernel, one warp per (token, head)."""
     v_dim = head_dim if v_dim is None else v_dim
-    if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64 or v_dim != head_dim or (keep_first and window):
-        # (kept first keys behind a window, and values of another size than the keys, are the exact kernel's alone)
+    keep_first = keep_first if window else 0
+    if not _tensor_core_attention(qkv.dtype, head_dim) or nq // nkv > 64 or v_dim != head_dim:
+        # (values of another size than the keys are the exact kernel's alone)
         return attention_generic(qkv, lane.k, lane.v, lane.block_table, ctx.token_req, ctx.positions, out, nq, nkv,
                                  head_dim, lane.page_size, scale, window, keep_first if window else 0, v_dim)
     _cuda(qkv, out, lane.k, lane.v, lane.block_table)
@@ -655,18 +662,18 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         fork, join = _side_events(qkv.device)
         fork.record(main)
         side.wait_event(fork)
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first)
         with torch.cuda.stream(side):
             attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0))
+                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first)
             join.record(side)
         main.wait_event(join)
         return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0))
+                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first)
     if plan["tiles"] is not None:
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"))
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first)
     return out
 
 

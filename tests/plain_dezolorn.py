@@ -69,6 +69,12 @@ def visible(i: int, j: int, size: int, keep_first: int) -> bool:
     return j <= i and (i - j < size or j < keep_first)
 
 
+def visible_mask(T: int, size: int, keep_first: int) -> torch.Tensor:
+    """[T, T] of `visible(i, j)`."""
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    return (j <= i) & ((i - j < size) | (j < keep_first))
+
+
 def attention_mixer(h: torch.Tensor, m: dict, w: dict, p: str, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
@@ -81,10 +87,10 @@ def attention_mixer(h: torch.Tensor, m: dict, w: dict, p: str, eps: float) -> to
     v = v.view(T, G, V)
     size, keep = int(m["mask"]["size"]), int(m["mask"]["keep_first"])
     out = torch.zeros(T, H, V, dtype=h.dtype)
+    mask = visible_mask(T, size, keep)
     for hd in range(H):
         g = hd // (H // G)
         s = (q[:, hd] @ k[:, g].T) * float(m["scale"])
-        mask = torch.tensor([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
         s = s.masked_fill(~mask, float("-inf"))
         out[:, hd] = torch.softmax(s, dim=-1) @ v[:, g]
     return out.reshape(T, H * V) @ w[p + "o"].T

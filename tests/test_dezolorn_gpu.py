@@ -187,6 +187,27 @@ def test_window_edges_and_kept_keys(dtype, tmp_path):
         assert (got - want.float()).abs().max() <= lim, f"cuts {cuts}"
 
 
+@pytest.mark.parametrize("dim,size,keep,heads,kv_heads,page", [(64, 80, 5, 8, 2, 16), (128, 200, 70, 4, 4, 8), (32, 64, 64, 6, 1, 16),
+                                                               (64, 130, 1, 2, 1, 32)])
+def test_tensor_core_attention_with_a_window_and_kept_keys(dim, size, keep, heads, kv_heads, page, tmp_path):
+    """Head sizes that the bfloat16 tensor-core kernels take, prompts that cross their tiles of 64 keys and 128 queries,
+    kept keys that fill more than a tile.  Portions run the prefill kernel, single tokens the decode kernel.  Each mask that
+    is off by one (the window or the kept keys, either way) moves the oracle at some positions by twice the tolerance."""
+    cfg = config([attention_layer(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, size=size, keep=keep, dims=dim // 2)], width=64,
+                 softcap=0.0, logit_scale=1.0)
+    runner, w = make(tmp_path, cfg, seed=13, dtype=torch.bfloat16, blocks=64, page=page)
+    ids = tokens(470, cfg["vocab"], 14)
+    want = plain.forward(cfg, w, ids)
+    for d_size, d_keep in ((-1, 0), (1, 0), (0, -1), (0, 1)):
+        other = json.loads(json.dumps(cfg))
+        other["layers"][0]["mixer"]["mask"] = {"size": size + d_size, "keep_first": keep + d_keep}
+        assert (plain.forward(other, w, ids) - want).abs().max() > 0.3, "the oracle does not feel the mask"
+    for cuts in ([470], [300, 2, 129, 30], [260] + [1] * 150 + [50]):
+        got = run_cut(runner, 0, ids, cuts)
+        err = (got - want.float()).abs().amax(-1)
+        assert err.max() <= 0.15, f"cuts {cuts[:4]}: position {int(err.argmax())} differs by {float(err.max())}"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_far_tokens_reach_through_the_state(dtype, tmp_path):
     """A slow decay keeps the first tokens in the state for hundreds of steps: changing token 0 must move the last
