@@ -20,6 +20,12 @@ so nothing is flushed between timed iterations.  Peaks come from MEASURED_PEAKS.
 file when present.
 
 `--impl reference` runs the same workloads on the unmodified reference engine (baseline/reference_arm.py).
+
+`--design dezolorn` measures another thing and leaves the above alone: prefill and decode throughput of Dezolorn models
+(windowed attention with kept first keys, retention, gated delta rule; random weights) at two sizes that resemble real
+layers, each beside a Llama model of equal width, feed-forward, heads and layer count, and every kernel of one prefill
+step and one decode step of both, timed alone and set against its own bound (bytes over the copy peak, tensor flops over
+the tensor peak, CUDA-core flops over the nominal float32 rate).
 """
 
 from __future__ import annotations
@@ -423,6 +429,181 @@ def run_ours(args) -> dict:
     }
 
 
+# ---- another design beside its closest sibling (--design) ---------------------------------------------------------------
+
+DESIGN_SIZES = {
+    # width, feed-forward, attention heads / kv heads / head size, state mixers' heads / q-k heads / head sizes, layers
+    "w2048": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, s_heads=16, s_kv=8, s_dim=128, s_vdim=128, layers=8),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, s_heads=32, s_kv=16, s_dim=128, s_vdim=128, layers=4),
+}
+DESIGN_VOCAB, DESIGN_WINDOW, DESIGN_KEEP = 32768, 1024, 4
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12  # CUDA cores: 148 SMs x 128 lanes x 2 flops x the top clock
+
+
+def dezolorn_config(sz: dict) -> dict:
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": sz["ff"]}, "mixer": {
+        "heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+        "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP},
+        "rot": {"dims": sz["dim"], "base": 500000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    retention = {"type": "retention", "mlp": {"kind": "dense", "ff": sz["ff"]}, "mixer": {
+        "heads": sz["s_heads"], "dim": sz["s_dim"], "vdim": sz["s_vdim"],
+        "decay": [1.0 - 2.0 ** -(5 + h % 8) for h in range(sz["s_heads"])], "rot": {"dims": sz["s_dim"], "base": 10000.0}}}
+    delta = {"type": "delta", "mlp": {"kind": "dense", "ff": sz["ff"]}, "mixer": {
+        "heads": sz["s_heads"], "kv_heads": sz["s_kv"], "dim": sz["s_dim"], "vdim": sz["s_vdim"], "conv": 4}}
+    pattern = [attention, retention, delta, attention]
+    return {"architecture": "Dezolorn", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6},
+            "layers": [pattern[i % 4] for i in range(sz["layers"])], "loop": {"start": 0, "stop": 0, "times": 1},
+            "logit_scale": 1.0, "logit_softcap": 30.0}
+
+
+def llama_sibling(sz: dict):
+    from nanospec_b200 import LlamaConfig
+
+    return LlamaConfig(vocab_size=DESIGN_VOCAB, hidden_size=sz["width"], intermediate_size=sz["ff"], num_hidden_layers=sz["layers"],
+                       num_attention_heads=sz["heads"], num_key_value_heads=sz["kv_heads"], head_dim=sz["dim"], rms_norm_eps=1e-6,
+                       rope_theta=500000.0, max_position_embeddings=8192, rope_scaling=None, tie_word_embeddings=False, eos_token_ids=())
+
+
+def kernel_bounds(kind: str, sz: dict, tokens: int, batch: int, context: int, pk: dict) -> dict[str, float]:
+    """Seconds that every kernel of one step needs at least, summed over the step's calls of it.  `tokens` > 0: a prompt of that
+    many tokens; otherwise `batch` requests decoding at `context` tokens."""
+    N = tokens or batch
+    H, L = sz["width"], sz["layers"]
+    bw, tc, cc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12, FP32_TFLOPS_NOMINAL * 1e12
+    nq, nkv, d = sz["heads"], sz["kv_heads"], sz["dim"]
+    norm = 12.0 * N * H / bw  # stream read and written in float32, branch read and result written in bfloat16
+    qkv = 2.0 * N * ((nq + nkv) * d * 2 + nkv * d + 2 * nkv * d) / bw
+    out: dict[str, float] = {}
+    if kind == "llama":
+        pairs = tokens * (tokens + 1) // 2 if tokens else 0
+        out["ns_add_rmsnorm"] = 2 * L * norm
+        out["ns_rope_kv_write"] = L * qkv
+        out["ns_attention_prefill_tc" if tokens else "ns_attention_decode_tma"] = \
+            L * (4.0 * nq * d * pairs / tc if tokens else 4.0 * batch * context * nkv * d / bw)
+        out["ns_swiglu"] = L * 6.0 * N * sz["ff"] / bw
+        return out
+    n_att, n_ret, n_del = (sum(1 for i in range(L) if i % 4 in kinds) for kinds in ((0, 3), (1,), (2,)))
+    sh, sk, sd, sv = sz["s_heads"], sz["s_kv"], sz["s_dim"], sz["s_vdim"]
+    seen = lambda p: min(p + 1, DESIGN_WINDOW) + max(0, min(DESIGN_KEEP, p + 1 - DESIGN_WINDOW))  # keys position p sees
+    out["ns_add_layernorm"] = 2 * L * norm
+    out["ns_qk_norm_rope_store"] = n_att * qkv
+    if tokens:
+        out["ns_attention_prefill_kept"] = n_att * 4.0 * nq * d * sum(seen(p) for p in range(tokens)) / tc
+    else:
+        out["ns_attention_decode_kept"] = n_att * 4.0 * batch * seen(context) * nkv * d / bw
+    out["ns_swiglu"] = L * 6.0 * N * sz["ff"] / bw
+    out["ns_rotary_prepare"] = n_ret * N * ((2 * sh * sd + sh * sv) * 2 + (2 * sh * sd + sh * sv) * 4) / bw
+    chan = 2 * sk * sd + sh * sv
+    out["ns_delta_prepare"] = n_del * N * (chan * 2 + (chan + 2 * sh) * 4) / bw
+    rec_in = lambda g: (2 * g * sd + sh * sv) * 4.0  # the float32 operands of one token
+    if tokens:  # the recurrence on CUDA cores: per token, head and state entry 5 flops (plain) or 7 (delta rule)
+        out["ns_linear_scan"] = (n_ret * 5.0 + n_del * 7.0) * tokens * sh * sd * sv / cc
+    else:       # the state read and written once per request
+        out["ns_linear_scan"] = (n_ret + n_del) * batch * (8.0 * sh * sd * sv) / bw + batch * (n_ret * rec_in(sh) + n_del * rec_in(sk)) / bw
+    out["ns_head_norm_gate"] = (n_ret + n_del) * N * sh * sv * 8.0 / bw
+    return out
+
+
+def design_engine(model, max_running: int, num_blocks: int, **kw):
+    from nanospec_b200 import Engine, EngineConfig
+
+    opts = dict(num_blocks=num_blocks, block_size=PAGE, max_running=max_running, max_admit=64, max_step_tokens=8192,
+                prefill_chunk=PREFILL_TOKENS)
+    opts.update(kw)
+    return Engine(model, EngineConfig(**opts))
+
+
+def time_kernels(model, tokens: int, batch: int, context: int) -> dict[str, tuple[int, float]]:
+    """Every entry point of one eager step, bracketed by events: a prompt of `tokens`, or `batch` requests that decode at `context`."""
+    import torch
+
+    from nanospec_b200.engine.step import ModelRunner, StepEntry
+    from nanospec_b200.ops import lib
+
+    runner = ModelRunner(model, num_blocks=max(batch, 1) * (-(-(context + PREFILL_TOKENS) // PAGE) + 2), block_size=PAGE, max_requests=max(batch, 1))
+    g = torch.Generator().manual_seed(5)
+    ids = lambda n: torch.randint(0, model.vocab_size, (n,), generator=g).tolist()
+    best: dict[str, tuple[int, float]] = {}
+    if tokens:
+        for it in range(4):
+            runner.begin(it)
+            if it:
+                lib.start_kernel_timing()
+            runner.step([StepEntry(it, ids(tokens), [tokens - 1])])
+            if it:
+                got = lib.stop_kernel_timing()
+                best = {k: (v[0], min(v[1], best.get(k, v)[1])) for k, v in got.items()}
+            runner.end(it)
+        return best
+    for b in range(batch):
+        runner.begin(b)
+    for at in range(0, context, PREFILL_TOKENS):  # the contexts, eight requests to a step
+        for b0 in range(0, batch, 8):
+            runner.step([StepEntry(b, ids(min(PREFILL_TOKENS, context - at)), []) for b in range(b0, min(batch, b0 + 8))])
+    for it in range(4):
+        if it:
+            lib.start_kernel_timing()
+        runner.step([StepEntry(b, ids(1), [0]) for b in range(batch)])
+        if it:
+            got = lib.stop_kernel_timing()
+            best = {k: (v[0], min(v[1], best.get(k, v)[1])) for k, v in got.items()}
+    return best
+
+
+def run_design(args) -> dict:
+    import torch
+
+    from nanospec_b200 import random_model
+
+    pk, pk_src = peaks()
+    out_sizes = {}
+    for name, sz in DESIGN_SIZES.items():
+        row = {}
+        for kind in ("dezolorn", "llama"):
+            cfg = dezolorn_config(sz) if kind == "dezolorn" else llama_sibling(sz)
+            model = random_model(cfg, seed=1, device="cuda", dtype=torch.bfloat16)
+            pages_per_req = -(-(CONTEXT + args.repeats * args.steps + args.warmup + 64) // PAGE)
+            eng = design_engine(model, 64, max(64 * pages_per_req, -(-PREFILL_TOKENS // PAGE) + 8) + 8)
+            rec = {}
+            for b in (8, 64):
+                pt = time_decode(eng, b, args.steps, args.warmup, args.repeats)
+                rec[f"decode_b{b}_tok_s"] = round(b * 1000.0 / pt["ms"], 1)
+                rec[f"decode_b{b}_ms"] = round(pt["ms"], 4)
+                rec[f"decode_b{b}_clocks"] = {"sm_mhz": pt["clocks"].get("sm_mhz"), "reasons": pt["clocks"].get("reasons")}
+                if b == 8 and kind == "dezolorn" and name == "w4096":
+                    headline = pt
+            pre_ms, pre_clocks = time_prefill(eng, warmup=3, iters=5)
+            rec["prefill_tok_s"] = round(PREFILL_TOKENS * 1000.0 / pre_ms, 1)
+            rec["prefill_ms"] = round(pre_ms, 3)
+            rec["prefill_clocks"] = {"sm_mhz": pre_clocks.get("sm_mhz"), "reasons": pre_clocks.get("reasons")}
+            del eng
+            torch.cuda.empty_cache()
+            kernels = {}
+            for what, tokens, batch in (("prefill", PREFILL_TOKENS, 0), ("decode_b64", 0, 64)):
+                timed = time_kernels(model, tokens, batch, CONTEXT)
+                bounds = kernel_bounds(kind, sz, tokens, batch, CONTEXT, pk)
+                kernels[what] = {k: {"calls": n, "ms": round(ms, 4), "bound_ms": round(bounds[k] * 1e3, 4) if k in bounds else None,
+                                     "frac": round(bounds[k] * 1e3 / ms, 4) if k in bounds and ms > 0 else None}
+                                 for k, (n, ms) in sorted(timed.items(), key=lambda kv: -kv[1][1])}
+            rec["kernels"] = kernels
+            row[kind] = rec
+            del model
+            torch.cuda.empty_cache()
+        out_sizes[name] = row
+    value = out_sizes["w4096"]["dezolorn"]["decode_b8_tok_s"]
+    return {
+        "metric": "decode tok/s (Dezolorn, width 4,096, 4 layers, batch 8, 1,024-token context)", "value": value, "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": out_sizes["w4096"]["dezolorn"]["decode_b8_ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform random token ids, random weights",
+        "config": {"design": "dezolorn beside llama", "sizes": DESIGN_SIZES, "vocab": DESIGN_VOCAB, "window": DESIGN_WINDOW,
+                   "keep_first": DESIGN_KEEP, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "page": PAGE, "cuda_graphs": True,
+                   "peaks": pk_src, "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1),
+                   "l2": "the weights of every step are larger than L2"},
+        "gpu_launches": headline["launches"], "clocks": headline["clocks"], "sizes": out_sizes,
+    }
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
 
@@ -439,6 +620,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"])
     ap.add_argument("--no-workloads", action="store_true", help="leave out the 3B continuous-batching and 1B mixed workloads")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--design", choices=["dezolorn"], help="measure this design beside the Llama model of equal size instead")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.repeats = max(1, args.repeats)
@@ -446,7 +628,7 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    out = run_reference(args) if args.impl == "reference" else run_design(args) if args.design else run_ours(args)
     print(json.dumps(out), flush=True)
     return 0
 

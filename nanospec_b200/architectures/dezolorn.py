@@ -19,7 +19,7 @@ def _mixer(kind: str, m: dict, width: int, eps: float) -> PartSpec:
         return PartSpec("gqa_attention", {
             "hidden": width, "heads": int(m["heads"]), "kv_heads": int(m["kv_heads"]), "head_dim": int(m["dim"]),
             "v_dim": int(m["vdim"]), "window": int(m["mask"]["size"]), "keep_first": int(m["mask"]["keep_first"]),
-            "scale": float(m["scale"]), "qk_norm": {"eps": eps}, "position": position,
+            "scale": float(m["scale"]), "qk_norm": {"eps": eps}, "position": position, "wide_weights": True,
             "names": {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm"}})
     if kind == "retention":
         rot = m["rot"]

@@ -30,7 +30,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ qo_indptr, __nv_bfloat16* __restrict__ out, int o_stride,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                         const int* __restrict__ rows, int nq, int nkv, int page_size, float scale, int window,
-                        int n_splits, int head_tiles, int keep_first) {
+                        int n_splits, int head_tiles, int keep_first, int wide_weights) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -151,6 +151,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 }
             uint32_t pa[4] = {ns_pack_bf16(s[0][0], s[0][1]), ns_pack_bf16(s[0][2], s[0][3]),
                               ns_pack_bf16(s[1][0], s[1][1]), ns_pack_bf16(s[1][2], s[1][3])};
+            uint32_t pr[4] = {0u, 0u, 0u, 0u};
+            if (wide_weights) {
+                pr[0] = ns_pack_bf16_rest(s[0][0], s[0][1]); pr[1] = ns_pack_bf16_rest(s[0][2], s[0][3]);
+                pr[2] = ns_pack_bf16_rest(s[1][0], s[1][1]); pr[3] = ns_pack_bf16_rest(s[1][2], s[1][3]);
+            }
             if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {  // some row's maximum moved
 #pragma unroll
                 for (int nb = 0; nb < D / 8; ++nb) {
@@ -164,6 +169,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                 ns_ldmatrix_x4_trans(vf, Tile::at(vs, warp * 16 + (mat & 1) * 8 + r8, nb2 * 16 + (mat >> 1) * 8));
                 ns_mma_bf16(o[2 * nb2], pa, vf[0], vf[1]);
                 ns_mma_bf16(o[2 * nb2 + 1], pa, vf[2], vf[3]);
+                if (wide_weights) {  // the part of each weight that rounding to bfloat16 dropped
+                    ns_mma_bf16(o[2 * nb2], pr, vf[0], vf[1]);
+                    ns_mma_bf16(o[2 * nb2 + 1], pr, vf[2], vf[3]);
+                }
             }
         }
     }
@@ -268,7 +277,7 @@ template <int D, int kStages>
 int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0) {
     constexpr int S = NsTile<D>::kStride;
     const size_t tiles = (size_t)(16 + 2 * kStages * kTileKeys) * S * sizeof(__nv_bfloat16);
     const size_t scratch = (size_t)(4 * 16 * D + 128) * sizeof(float);  // the warps' partial results reuse the k/v stages
@@ -283,7 +292,7 @@ int launch_decode_stages(const void* q, int q_stride, const void* k_cache, const
     NS_LAUNCH((attention_decode_kernel<D, kStages>), grid, kThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, token_req, positions, qo_indptr, (__nv_bfloat16*)out, o_stride, part_o, part_ml, counters, rows, nq,
-        nkv, page_size, scale, window, n_splits, head_tiles, keep_first);
+        nkv, page_size, scale, window, n_splits, head_tiles, keep_first, wide_weights);
     NS_CHECK_LAUNCH("ns_attention_decode");
     return NS_OK;
 }
@@ -294,14 +303,14 @@ template <int D>
 int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int table_stride, const int* token_req, const int* positions, const int* qo_indptr, void* out,
                   int o_stride, float* part_o, float* part_ml, int* counters, const int* rows, int n_tokens, int nq,
-                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0) {
+                  int nkv, int page_size, float scale, int window, int n_splits, cudaStream_t stream, int keep_first = 0, int wide_weights = 0) {
     if (g_decode_stages == 2)
         return launch_decode_stages<D, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                           qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                          page_size, scale, window, n_splits, stream, keep_first);
+                                          page_size, scale, window, n_splits, stream, keep_first, wide_weights);
     return launch_decode_stages<D, 3>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,
                                       qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,
-                                      page_size, scale, window, n_splits, stream, keep_first);
+                                      page_size, scale, window, n_splits, stream, keep_first, wide_weights);
 }
 
 }  // namespace
@@ -327,11 +336,12 @@ NS_API int ns_attention_decode_scratch(int n_tokens, int nq, int nkv, int d, int
 // launch; every launch leaves it zero again.  `rows` (optional) lists the token rows to work on
 // (n_tokens of them); without it the tokens are 0 .. n_tokens-1.
 // `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
+// `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
 NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                     const int* block_table, int table_stride, const int* token_req, const int* positions,
                                     const int* qo_indptr, void* out, int o_stride, float* part_o, float* part_ml,
                                     int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
-                                    float scale, int window, int keep_first, int n_splits, cudaStream_t stream) {
+                                    float scale, int window, int keep_first, int wide_weights, int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_decode: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
@@ -345,7 +355,7 @@ NS_API int ns_attention_decode_kept(const void* q, int q_stride, const void* k_c
     case DD:                                                                                                           \
         return launch_decode<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions,       \
                                  qo_indptr, out, o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv,         \
-                                 page_size, scale, window, n_splits, stream, keep_first);
+                                 page_size, scale, window, n_splits, stream, keep_first, wide_weights);
     switch (d) {
         NS_DECODE_CASE(16) NS_DECODE_CASE(32) NS_DECODE_CASE(48) NS_DECODE_CASE(64)
         NS_DECODE_CASE(80) NS_DECODE_CASE(96) NS_DECODE_CASE(112) NS_DECODE_CASE(128)
@@ -360,7 +370,7 @@ NS_API int ns_attention_decode(const void* q, int q_stride, const void* k_cache,
                                int* counters, const int* rows, int n_tokens, int nq, int nkv, int d, int page_size,
                                float scale, int window, int n_splits, cudaStream_t stream) {
     return ns_attention_decode_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, token_req, positions, qo_indptr, out,
-                                    o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, d, page_size, scale, window, 0,
+                                    o_stride, part_o, part_ml, counters, rows, n_tokens, nq, nkv, d, page_size, scale, window, 0, 0,
                                     n_splits, stream);
 }
 

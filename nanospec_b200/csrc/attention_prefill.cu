@@ -26,7 +26,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, const int* __restrict__ positions, const int* __restrict__ qo_indptr,
                          const int* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int o_stride, int nq, int nkv,
-                         int page_size, float scale, int window, int keep_first) {
+                         int page_size, float scale, int window, int keep_first, int wide_weights) {
     ns_pdl_launch_dependents();  // the next kernel may be scheduled now; it waits for this one before it reads
     ns_pdl_wait();               // everything below sees the previous kernel's results
     using Tile = NsTile<D>;
@@ -171,12 +171,22 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                 uint32_t pa[4] = {ns_pack_bf16(s[2 * kb16][0], s[2 * kb16][1]), ns_pack_bf16(s[2 * kb16][2], s[2 * kb16][3]),
                                   ns_pack_bf16(s[2 * kb16 + 1][0], s[2 * kb16 + 1][1]),
                                   ns_pack_bf16(s[2 * kb16 + 1][2], s[2 * kb16 + 1][3])};
+                uint32_t pr[4] = {0u, 0u, 0u, 0u};
+                if (wide_weights) {
+                    pr[0] = ns_pack_bf16_rest(s[2 * kb16][0], s[2 * kb16][1]); pr[1] = ns_pack_bf16_rest(s[2 * kb16][2], s[2 * kb16][3]);
+                    pr[2] = ns_pack_bf16_rest(s[2 * kb16 + 1][0], s[2 * kb16 + 1][1]);
+                    pr[3] = ns_pack_bf16_rest(s[2 * kb16 + 1][2], s[2 * kb16 + 1][3]);
+                }
 #pragma unroll
                 for (int nb2 = 0; nb2 < D / 16; ++nb2) {
                     uint32_t vf[4];
                     ns_ldmatrix_x4_trans(vf, Tile::at(vs, kb16 * 16 + (mat & 1) * 8 + r8, nb2 * 16 + (mat >> 1) * 8));
                     ns_mma_bf16(o[2 * nb2], pa, vf[0], vf[1]);
                     ns_mma_bf16(o[2 * nb2 + 1], pa, vf[2], vf[3]);
+                    if (wide_weights) {  // the part of each weight that rounding to bfloat16 dropped
+                        ns_mma_bf16(o[2 * nb2], pr, vf[0], vf[1]);
+                        ns_mma_bf16(o[2 * nb2 + 1], pr, vf[2], vf[3]);
+                    }
                 }
             }
         }
@@ -207,7 +217,7 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                    int table_stride, const int* positions, const int* qo_indptr, const int* tiles, int n_tiles,
                    void* out, int o_stride, int nq, int nkv, int page_size, float scale, int window,
-                   cudaStream_t stream, int keep_first = 0) {
+                   cudaStream_t stream, int keep_first = 0, int wide_weights = 0) {
     constexpr int S = NsTile<D>::kStride;
     const size_t smem = (size_t)(kTileQ + 4 * kTileKeys) * S * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -218,7 +228,7 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
     dim3 grid(n_tiles, nq);
     NS_LAUNCH((attention_prefill_kernel<D>), grid, kPrefillThreads, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
-        table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first);
+        table_stride, positions, qo_indptr, tiles, (__nv_bfloat16*)out, o_stride, nq, nkv, page_size, scale, window, keep_first, wide_weights);
     NS_CHECK_LAUNCH("ns_attention_prefill");
     return NS_OK;
 }
@@ -228,10 +238,11 @@ int launch_prefill(const void* q, int q_stride, const void* k_cache, const void*
 // tiles: int32 [n_tiles, 2] = (request, offset of the tile's first token among the request's
 // tokens of this step, a multiple of 128).  bfloat16 only; head_dim a multiple of 16 up to 128.
 // `keep_first` > 0 with a window: the first so many keys of a request stay visible behind the window.
+// `wide_weights`: the softmax weights meet the values as pairs of bfloat16 (rounded + dropped part), about 16 bits each.
 NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                      const int* block_table, int table_stride, const int* positions, const int* qo_indptr,
                                      const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
-                                     int page_size, float scale, int window, int keep_first, cudaStream_t stream) {
+                                     int page_size, float scale, int window, int keep_first, int wide_weights, cudaStream_t stream) {
     if (n_tiles <= 0) return NS_OK;
     if (keep_first < 0 || window < 0) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_prefill: window=%d keep_first=%d", window, keep_first);
     if (window == 0) keep_first = 0;
@@ -244,7 +255,7 @@ NS_API int ns_attention_prefill_kept(const void* q, int q_stride, const void* k_
 #define NS_PREFILL_CASE(DD)                                                                                          \
     case DD:                                                                                                         \
         return launch_prefill<DD>(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr,   \
-                                  tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first);
+                                  tiles, n_tiles, out, o_stride, nq, nkv, page_size, scale, window, stream, keep_first, wide_weights);
     switch (d) {
         NS_PREFILL_CASE(16) NS_PREFILL_CASE(32) NS_PREFILL_CASE(48) NS_PREFILL_CASE(64)
         NS_PREFILL_CASE(80) NS_PREFILL_CASE(96) NS_PREFILL_CASE(112) NS_PREFILL_CASE(128)
@@ -258,5 +269,5 @@ NS_API int ns_attention_prefill(const void* q, int q_stride, const void* k_cache
                                 const int* tiles, int n_tiles, void* out, int o_stride, int nq, int nkv, int d,
                                 int page_size, float scale, int window, cudaStream_t stream) {
     return ns_attention_prefill_kept(q, q_stride, k_cache, v_cache, block_table, table_stride, positions, qo_indptr, tiles, n_tiles,
-                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, stream);
+                                     out, o_stride, nq, nkv, d, page_size, scale, window, 0, 0, stream);
 }

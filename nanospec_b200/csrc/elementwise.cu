@@ -125,7 +125,9 @@ add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ branch, cons
 
 // Vector variant for widths that are a multiple of 8 with 16-byte aligned rows: every thread owns
 // CHUNKS groups of 8 consecutive elements, read and written with 16-byte accesses.
-template <typename T, int THREADS, int CHUNKS>
+// CENTERED: the layer norm without bias instead - the mean is taken off first and the variance is the mean of the
+// squared deviations (a second sum over the values, which are in registers).
+template <typename T, int THREADS, int CHUNKS, bool CENTERED = false>
 __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, const float* __restrict__ gain,
                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps, int write_resid) {
@@ -159,7 +161,19 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ branch, 
                 if (write_resid) st8(r + h, v[c]);
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ss += v[c][i] * v[c][i];
+            for (int i = 0; i < 8; ++i) ss += CENTERED ? v[c][i] : v[c][i] * v[c][i];
+        }
+    }
+    if (CENTERED) {
+        const float mean = ns_block_sum(ss, scratch) / (float)hidden;
+        ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int h = (threadIdx.x + c * THREADS) * 8;
+            if (h < hidden) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { v[c][i] -= mean; ss += v[c][i] * v[c][i]; }
+            }
         }
     }
     const float inv = rsqrtf(ns_block_sum(ss, scratch) / (float)hidden + eps);
@@ -369,6 +383,21 @@ static int launch_add_layernorm(float* resid, const void* branch, const float* g
             NS_CUDA(cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             raised = 200 * 1024;
         }
+    }
+    const bool aligned = hidden % 8 == 0 && (((uintptr_t)resid | (uintptr_t)branch | (uintptr_t)gain | (uintptr_t)out) % 16 == 0);
+    if (aligned && hidden >= 1024 && hidden <= 16384) {  // which kernel runs depends on the width and alignment only, never on the batch
+        const T* b = (const T*)branch;
+        T* o = (T*)out;
+        if (hidden <= 2048)
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 128, 2, true>), n_rows, 128, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
+        else if (hidden <= 4096)
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 256, 2, true>), n_rows, 256, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
+        else if (hidden <= 8192)
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 512, 2, true>), n_rows, 512, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
+        else
+            NS_LAUNCH((add_rmsnorm_vec_kernel<T, 1024, 2, true>), n_rows, 1024, 0, stream, resid, b, gain, o, rows, hidden, eps, write_resid);
+        NS_CHECK_LAUNCH("ns_add_layernorm");
+        return NS_OK;
     }
     NS_LAUNCH((add_layernorm_kernel<T>), n_rows, 256, smem, stream, resid, (const T*)branch, gain, (T*)out, rows, hidden, eps,
               write_resid);

@@ -52,6 +52,14 @@ __device__ __forceinline__ uint32_t ns_pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// What rounding to bfloat16 dropped from a pair: (lo - bf16(lo), hi - bf16(hi)), itself as bfloat16.  A weight given
+// to the tensor cores as the pair (rounded, dropped) carries about 16 bits of its float value instead of 8.
+__device__ __forceinline__ uint32_t ns_pack_bf16_rest(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    const float2 f = __bfloat1622float2(v);
+    return ns_pack_bf16(lo - f.x, hi - f.y);
+}
+
 // Tiles in shared memory are rows of D bf16 padded by 8 elements (16 bytes): for D a multiple
 // of 16 the row stride is an odd number of 16-byte units, so the 8 rows that one ldmatrix phase
 // reads fall in 8 different 16-byte bank groups.

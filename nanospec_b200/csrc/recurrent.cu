@@ -141,10 +141,23 @@ rotary_prepare_kernel(const T* __restrict__ proj, int ld_proj, const int* __rest
 }
 
 // ---------------------------------------------------------------------------------------
-// the scan.  grid (request, head, 32 columns); 128 threads: lane = part * 8 + column, part 0..3 holds rows
-// part*R .. part*R + R - 1 of its column.  q and k heads are shared by H / G heads each.
-// gate: per token and head (row stride ld) or null, then `decay[h]` is used; beta: null selects the plain rule.
+// the scan.  grid (request, head, columns / COLS); 128 threads.  A column of S is held by LPC lanes (4 or 8) of one
+// warp, R = Dp / LPC rows each: lane = part * (32 / LPC) + column, part p holds rows p*R .. p*R + R - 1.  The operands
+// of 16 tokens at a time (8 for the widest heads) are brought to shared memory with cp.async, two stages deep, so the
+// walk over the tokens waits for memory once per stage and not once per token; a row of q or k lies there in LPC
+// segments of R + 4 floats (the parts' 16-byte reads then fall into different banks).
+// q and k heads are shared by H / G heads each.  gate: per token and head (row stride ld) or null, then `decay[h]` is
+// used; beta: null selects the plain rule.
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int R>
 __device__ __forceinline__ void load_row(const float* p, float (&x)[R]) {
 #pragma unroll
@@ -154,7 +167,7 @@ __device__ __forceinline__ void load_row(const float* p, float (&x)[R]) {
     }
 }
 
-template <int R>
+template <int R, int LPC>
 __device__ __forceinline__ float dot_row(const float (&s)[R], const float (&x)[R]) {
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // four partial sums, always combined in the same order
 #pragma unroll
@@ -163,12 +176,22 @@ __device__ __forceinline__ float dot_row(const float (&s)[R], const float (&x)[R
         a2 = fmaf(s[i + 2], x[i + 2], a2); a3 = fmaf(s[i + 3], x[i + 3], a3);
     }
     float v = (a0 + a1) + (a2 + a3);
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    v += __shfl_xor_sync(0xffffffffu, v, 16);
+#pragma unroll
+    for (int off = 32 / LPC; off < 32; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
     return v;
 }
 
-template <int R>
+template <int R, int LPC>
+struct ScanShape {
+    static constexpr int kCols = 128 / LPC;                 // columns per block
+    static constexpr int kDp = R * LPC;
+    static constexpr int kTokens = kDp > 128 ? 8 : 16;      // tokens per stage
+    static constexpr int kSeg = R + 4, kRow = LPC * kSeg;   // a staged row of q or k
+    static constexpr int kStage = kTokens * (2 * kRow + kCols + 2);  // floats: q rows, k rows, v slices, gates, betas
+    static constexpr size_t kBytes = 2 * (size_t)kStage * sizeof(float);
+};
+
+template <int R, int LPC>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                    const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ decay, int ld,
@@ -176,65 +199,83 @@ linear_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, con
                    const int* __restrict__ state_slot, float* __restrict__ out, int ld_out, int H, int G, int D, int V) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
+    using Sh = ScanShape<R, LPC>;
+    constexpr int CW = 32 / LPC;  // columns per warp
+    extern __shared__ __align__(16) float scan_smem[];
     const int b = blockIdx.x, h = blockIdx.y;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = lane >> 3;
-    const int e = blockIdx.z * 32 + warp * 8 + (lane & 7);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int part = lane / CW;
+    const int col = warp * CW + (lane % CW);       // column within the block
+    const int e0 = blockIdx.z * Sh::kCols, e = e0 + col;
     const bool active = e < V;
     const int start = qo_indptr[b], end = qo_indptr[b + 1];
     if (end <= start) return;
-    constexpr int Dp = 4 * R;
     const int hk = h / (H / G);
     float* S_mem = state + (long long)state_slot[b] * state_floats + ((long long)h * D + part * R) * V + e;
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) S[r] = (active && part * R + r < D) ? S_mem[(size_t)r * V] : 0.f;
-    const float* qp = q + (size_t)hk * Dp + part * R;
-    const float* kp = k + (size_t)hk * Dp + part * R;
     const float fixed = decay ? decay[h] : 1.f;
-    constexpr bool kAhead = R <= 32;  // wider heads would not keep two tokens' operands in registers
-    constexpr int RN = kAhead ? R : 4;
-    float kn[RN], qn[RN], vn = 0.f, gn = fixed, bn = 0.f;
-    if (kAhead) {
-        load_row<RN>(kp + (size_t)start * ld, kn);
-        load_row<RN>(qp + (size_t)start * ld, qn);
-        vn = active ? v[(size_t)start * ld + h * V + e] : 0.f;
-        if (gate) gn = gate[(size_t)start * ld + h];
-        if (beta) bn = beta[(size_t)start * ld + h];
-    }
-    for (int n = start; n < end; ++n) {
-        float kc[R], qc[R];
-        float vc, gc, bc;
-        if (kAhead) {
+    const float* qh = q + (size_t)hk * Sh::kDp;
+    const float* kh = k + (size_t)hk * Sh::kDp;
+    const float* vh = v + (size_t)h * V + e0;
+    const int n_cols = min(Sh::kCols, V - e0);
+
+    auto issue = [&](int chunk) {  // the operands of tokens chunk*kTokens .. of this request into stage chunk & 1
+        float* st = scan_smem + (size_t)(chunk & 1) * Sh::kStage;
+        const int n0 = start + chunk * Sh::kTokens, cnt = min(Sh::kTokens, end - n0);
+        constexpr int kPieces = Sh::kDp / 4;  // 16-byte pieces of a row
+        for (int i = tid; i < cnt * kPieces; i += 128) {
+            const int t = i / kPieces, j = i - t * kPieces;
+            const int p = (4 * j) / R, within = 4 * j - p * R;
+            cp_async16(st + t * Sh::kRow + p * Sh::kSeg + within, qh + (size_t)(n0 + t) * ld + 4 * j);
+            cp_async16(st + Sh::kTokens * Sh::kRow + t * Sh::kRow + p * Sh::kSeg + within, kh + (size_t)(n0 + t) * ld + 4 * j);
+        }
+        float* sv = st + 2 * Sh::kTokens * Sh::kRow;
+        for (int i = tid; i < cnt * n_cols; i += 128) {
+            const int t = i / n_cols, c = i - t * n_cols;
+            cp_async4(sv + t * Sh::kCols + c, vh + (size_t)(n0 + t) * ld + c);
+        }
+        float* sg = sv + Sh::kTokens * Sh::kCols;
+        if (tid < cnt) {
+            if (gate) cp_async4(sg + tid, gate + (size_t)(n0 + tid) * ld + h);
+            if (beta) cp_async4(sg + Sh::kTokens + tid, beta + (size_t)(n0 + tid) * ld + h);
+        }
+    };
+
+    const int n_chunks = (end - start + Sh::kTokens - 1) / Sh::kTokens;
+    issue(0);
+    cp_async_commit();
+    for (int c = 0; c < n_chunks; ++c) {
+        if (c + 1 < n_chunks) issue(c + 1);
+        cp_async_commit();
+        cp_async_wait<1>();  // stage c has landed (the group after it may still travel)
+        __syncthreads();
+        const float* st = scan_smem + (size_t)(c & 1) * Sh::kStage;
+        const float* sv = st + 2 * Sh::kTokens * Sh::kRow;
+        const float* sg = sv + Sh::kTokens * Sh::kCols;
+        const int n0 = start + c * Sh::kTokens, cnt = min(Sh::kTokens, end - n0);
+        for (int t = 0; t < cnt; ++t) {
+            float kc[R], qc[R];
+            load_row<R>(st + Sh::kTokens * Sh::kRow + t * Sh::kRow + part * Sh::kSeg, kc);
+            load_row<R>(st + t * Sh::kRow + part * Sh::kSeg, qc);
+            const float vc = sv[t * Sh::kCols + col];
+            const float gc = gate ? sg[t] : fixed;
+            if (beta) {
+                const float bc = sg[Sh::kTokens + t];
 #pragma unroll
-            for (int r = 0; r < R; ++r) { kc[r] = kn[r % RN]; qc[r] = qn[r % RN]; }
-            vc = vn; gc = gn; bc = bn;
-            if (n + 1 < end) {  // the next token's operands travel while this one is computed
-                load_row<RN>(kp + (size_t)(n + 1) * ld, kn);
-                load_row<RN>(qp + (size_t)(n + 1) * ld, qn);
-                vn = active ? v[(size_t)(n + 1) * ld + h * V + e] : 0.f;
-                if (gate) gn = gate[(size_t)(n + 1) * ld + h];
-                if (beta) bn = beta[(size_t)(n + 1) * ld + h];
+                for (int r = 0; r < R; ++r) S[r] *= gc;
+                const float u = bc * (vc - dot_row<R, LPC>(S, kc));
+#pragma unroll
+                for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], u, S[r]);
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], vc, gc * S[r]);
             }
-        } else {
-            load_row<R>(kp + (size_t)n * ld, kc);
-            load_row<R>(qp + (size_t)n * ld, qc);
-            vc = active ? v[(size_t)n * ld + h * V + e] : 0.f;
-            gc = gate ? gate[(size_t)n * ld + h] : fixed;
-            bc = beta ? beta[(size_t)n * ld + h] : 0.f;
+            const float o = dot_row<R, LPC>(S, qc);
+            if (active && part == 0) out[(size_t)(n0 + t) * ld_out + h * V + e] = o;
         }
-        if (beta) {
-#pragma unroll
-            for (int r = 0; r < R; ++r) S[r] *= gc;
-            const float u = bc * (vc - dot_row<R>(S, kc));
-#pragma unroll
-            for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], u, S[r]);
-        } else {
-#pragma unroll
-            for (int r = 0; r < R; ++r) S[r] = fmaf(kc[r], vc, gc * S[r]);
-        }
-        const float o = dot_row<R>(S, qc);
-        if (active && part == 0) out[(size_t)n * ld_out + h * V + e] = o;
+        __syncthreads();  // the stage may be refilled
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -318,33 +359,56 @@ NS_API int ns_rotary_prepare(const void* proj, int ld_proj, const int* positions
     return NS_OK;
 }
 
-// Rows per lane that the scan is compiled for; a head of D features takes the smallest R with 4 * R >= D.
+// The width that the scan pads a head of D features to: the smallest of 16, 32, 64, 128, 256 that holds it.
 NS_API int ns_linear_scan_rows(int D) {
     for (int r : {4, 8, 16, 32, 64})
         if (4 * r >= D) return r;
     return 0;
 }
 
+namespace {
+template <int R, int LPC>
+int launch_scan(const float* q, const float* k, const float* v, const float* gate, const float* beta, const float* decay, int ld,
+                float* state, long long state_floats, const int* qo_indptr, const int* state_slot, float* out, int ld_out,
+                int n_requests, int H, int G, int D, int V, cudaStream_t stream) {
+    using Sh = ScanShape<R, LPC>;
+    static bool configured = false;
+    if (!configured && Sh::kBytes > 48 * 1024) {
+        NS_CUDA(cudaFuncSetAttribute(linear_scan_kernel<R, LPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::kBytes));
+        configured = true;
+    }
+    const int col_blocks = (V + Sh::kCols - 1) / Sh::kCols;
+    if (H > 65535 || col_blocks > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: %d heads of %d columns exceed the grid", H, V);
+    NS_LAUNCH((linear_scan_kernel<R, LPC>), dim3(n_requests, H, col_blocks), 128, Sh::kBytes, stream, q, k, v, gate, beta, decay, ld,
+              state, state_floats, qo_indptr, state_slot, out, ld_out, H, G, D, V);
+    NS_CHECK_LAUNCH("ns_linear_scan");
+    return NS_OK;
+}
+}  // namespace
+
+// `longest`: the most tokens any request brings to this step (1 for decoding).  Long walks over few columns take eight lanes
+// per column instead of four: twice the blocks and half the work per token and lane.
 NS_API int ns_linear_scan(const float* q, const float* k, const float* v, const float* gate, const float* beta, const float* decay,
                           int ld, float* state, long long state_floats, const int* qo_indptr, const int* state_slot, float* out,
-                          int ld_out, int n_requests, int H, int G, int D, int V, cudaStream_t stream) {
+                          int ld_out, int n_requests, int H, int G, int D, int V, int longest, int n_sms, cudaStream_t stream) {
     if (n_requests <= 0) return NS_OK;
-    const int R = ns_linear_scan_rows(D);
-    if (!R) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: a head of %d features (at most 256)", D);
+    const int R4 = ns_linear_scan_rows(D);
+    if (!R4) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: a head of %d features (at most 256)", D);
     if (G < 1 || H % G) NS_FAIL(NS_ERR_ARGUMENT, "ns_linear_scan: %d heads over %d key heads", H, G);
     if (!gate && !decay) NS_FAIL(NS_ERR_ARGUMENT, "ns_linear_scan: neither a gate per token nor a decay per head");
     if (ld % 4 || ((uintptr_t)q | (uintptr_t)k) % 16) NS_FAIL(NS_ERR_ARGUMENT, "ns_linear_scan: q and k rows must be 16-byte aligned");
-    if (H > 65535 || (V + 31) / 32 > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: %d heads of %d columns exceed the grid", H, V);
-    const dim3 grid(n_requests, H, (V + 31) / 32);
-#define NS_SCAN_CASE(RR)                                                                                                        \
-    case RR:                                                                                                                    \
-        NS_LAUNCH((linear_scan_kernel<RR>), grid, 128, 0, stream, q, k, v, gate, beta, decay, ld, state, state_floats, qo_indptr, \
-                  state_slot, out, ld_out, H, G, D, V);                                                                         \
-        break;
-    switch (R) { NS_SCAN_CASE(4) NS_SCAN_CASE(8) NS_SCAN_CASE(16) NS_SCAN_CASE(32) NS_SCAN_CASE(64) }
-#undef NS_SCAN_CASE
-    NS_CHECK_LAUNCH("ns_linear_scan");
-    return NS_OK;
+    const long long blocks4 = (long long)n_requests * H * ((V + 31) / 32);
+    const bool eight = longest >= 64 && R4 >= 8 && blocks4 < 4ll * (n_sms > 0 ? n_sms : 148);
+#define NS_SCAN_ARGS q, k, v, gate, beta, decay, ld, state, state_floats, qo_indptr, state_slot, out, ld_out, n_requests, H, G, D, V, stream
+    switch (R4) {
+        case 4: return launch_scan<4, 4>(NS_SCAN_ARGS);
+        case 8: return eight ? launch_scan<4, 8>(NS_SCAN_ARGS) : launch_scan<8, 4>(NS_SCAN_ARGS);
+        case 16: return eight ? launch_scan<8, 8>(NS_SCAN_ARGS) : launch_scan<16, 4>(NS_SCAN_ARGS);
+        case 32: return eight ? launch_scan<16, 8>(NS_SCAN_ARGS) : launch_scan<32, 4>(NS_SCAN_ARGS);
+        case 64: return eight ? launch_scan<32, 8>(NS_SCAN_ARGS) : launch_scan<64, 4>(NS_SCAN_ARGS);
+    }
+#undef NS_SCAN_ARGS
+    NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: head of %d features", D);
 }
 
 NS_API int ns_head_norm_gate(const float* o, int ld_o, const void* gate, int ld_gate, const float* gain, float eps, void* out,

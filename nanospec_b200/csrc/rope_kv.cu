@@ -236,7 +236,6 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
                           int write_kv) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
-    __shared__ float scratch[32];
     const int n = blockIdx.x;
     const int req = token_req[n];
     if (req < 0) return;
@@ -244,15 +243,34 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
     T* row = qkv + (size_t)n * row_stride;
     const int q_size = nq * d, k_size = nkv * d;
     float inv_q = 1.f, inv_k = 1.f;
-    if (q_gain) {
-        float ss = 0.f;
-        for (int e = threadIdx.x; e < q_size; e += blockDim.x) { const float x = ns_ld(row, e); ss += x * x; }
-        inv_q = rsqrtf(ns_block_sum(ss, scratch) / (float)q_size + eps);
-    }
-    if (k_gain) {
-        float ss = 0.f;
-        for (int e = threadIdx.x; e < k_size; e += blockDim.x) { const float x = ns_ld(row, q_size + e); ss += x * x; }
-        inv_k = rsqrtf(ns_block_sum(ss, scratch) / (float)k_size + eps);
+    if (q_gain || k_gain) {
+        // both sums of squares in one pass over the row (16-byte reads when the row allows), one exchange for the two
+        float ssq = 0.f, ssk = 0.f;
+        if (q_size % 8 == 0 && k_size % 8 == 0 && row_stride % 8 == 0 && (uintptr_t)qkv % 16 == 0 && sizeof(T) == 2) {
+            for (int c = threadIdx.x; c < (q_size + k_size) / 8; c += blockDim.x) {
+                float x[8];
+                ld8(row + c * 8, x);
+                float t = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t += x[i] * x[i];
+                if (c * 8 < q_size) ssq += t; else ssk += t;
+            }
+        } else {
+            for (int e = threadIdx.x; e < q_size + k_size; e += blockDim.x) {
+                const float x = ns_ld(row, e);
+                if (e < q_size) ssq += x * x; else ssk += x * x;
+            }
+        }
+        ssq = ns_warp_sum(ssq);
+        ssk = ns_warp_sum(ssk);
+        __shared__ float part[2][8];
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (lane == 0) { part[0][warp] = ssq; part[1][warp] = ssk; }
+        __syncthreads();  // also: every read of the row for the sums is done before anything is written back
+        ssq = ssk = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { ssq += part[0][w]; ssk += part[1][w]; }
+        if (q_gain) inv_q = rsqrtf(ssq / (float)q_size + eps);
+        if (k_gain) inv_k = rsqrtf(ssk / (float)k_size + eps);
     }
     size_t slot = 0;
     if (write_kv) {

@@ -526,7 +526,7 @@ def _cluster_decode_splits(blocks: int, max_kv_len: int | None) -> int:
 
 def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
                      window: int, rows: torch.Tensor | None, n_rows: int, max_kv_len: int | None,
-                     work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0) -> None:
+                     work: torch.Tensor | None = None, work_slots: int = 0, keep_first: int = 0, wide_weights: bool = False) -> None:
     """Split-KV decode attention for the requests that bring one token.  Head sizes 64 and 128 with
     pages of 8 to 64 tokens: TMA loads and a thread-block cluster per request and kv head
     (csrc/attention_decode_tma.cu); everything else: cp.async loads and a merge through global
@@ -540,7 +540,7 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
         keep_first = 0
     # (kept first keys behind a window are the cp.async kernel's: the TMA kernel loads whole pages in key order)
     if USE_CLUSTER_DECODE and head_dim in (64, 128) and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 2 == 0 \
-            and not keep_first:
+            and not keep_first and not wide_weights:
         n_splits = _cluster_decode_splits(n_rows * nkv * head_tiles, max_kv_len)
         if work is not None and window == 0:
             ws = ctx.workspace
@@ -574,18 +574,19 @@ def attention_decode(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, n
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
              ctx.qo_indptr.data_ptr(), out.data_ptr(), out.stride(0), part_o.data_ptr(), part_ml.data_ptr(),
              counters.data_ptr(), _ptr(rows), n_rows, nq, nkv, head_dim, lane.page_size, float(scale), int(window),
-             int(keep_first), n_splits, _stream())
+             int(keep_first), int(bool(wide_weights)), n_splits, _stream())
 
 
 PREFILL_TWO_HEADS = "auto"  # "always" / "never": tests run both kernels whatever the size of the grid
 
 
 def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-                      window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None, keep_first: int = 0) -> None:
+                      window: int, tiles: torch.Tensor, tiles_tc: torch.Tensor | None = None, keep_first: int = 0,
+                      wide_weights: bool = False) -> None:
     """Tensor-core attention for portions of prompts.  `tiles`: int32 [n, 2] of (request, offset
     among its tokens of this step).  Head sizes 64 and 128 with pages of 8 to 64 tokens and no window run
     on tcgen05 (csrc/attention_prefill_tc.cu); everything else on m16n8k16 (csrc/attention_prefill.cu)."""
-    if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 \
+    if USE_TCGEN05_ATTENTION and tiles_tc is not None and head_dim in (64, 128) and window == 0 and not wide_weights \
             and lane.page_size in (8, 16, 32, 64) and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
         # heads of 64: two query heads of a kv head to a block (four softmax warps per sub-partition keep the exponential
         # unit busier and the keys are read once for both) - once one head to a block would give more blocks than SMs
@@ -600,7 +601,7 @@ def attention_prefill(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, 
     lib.call("ns_attention_prefill_kept", qkv.data_ptr(), qkv.stride(0), lane.k.data_ptr(), lane.v.data_ptr(),
              lane.block_table.data_ptr(), lane.block_table.stride(0), ctx.positions.data_ptr(), ctx.qo_indptr.data_ptr(),
              tiles.data_ptr(), tiles.shape[0], out.data_ptr(), out.stride(0), nq, nkv, head_dim, lane.page_size,
-             float(scale), int(window), int(keep_first) if window else 0, _stream())
+             float(scale), int(window), int(keep_first) if window else 0, int(bool(wide_weights)), _stream())
 
 
 def _attention_plan(ctx) -> dict:
@@ -636,11 +637,13 @@ def _attention_plan(ctx) -> dict:
 
 
 def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int, head_dim: int, scale: float,
-              window: int = 0, keep_first: int = 0, v_dim: int | None = None) -> torch.Tensor:
+              window: int = 0, keep_first: int = 0, v_dim: int | None = None, wide_weights: bool = False) -> torch.Tensor:
     """Attention of the step's queries (the first nq*head_dim columns of `qkv`) over `lane`.
 
     bfloat16 with a head size that the tensor-core kernels take: the decode kernel for requests
-    that bring one token, the prefill kernel for the others.  float32, and head sizes those
+    that bring one token, the prefill kernel for the others.  `wide_weights`: the softmax weights meet the values
+    with about 16 bits each (two bfloat16 products per weight) instead of 8, for designs that state their weights in
+    float32; the m16n8k16 kernels have it.  float32, and head sizes those
     kernels refuse: the exact kernel, one warp per (token, head)."""
     v_dim = head_dim if v_dim is None else v_dim
     keep_first = keep_first if window else 0
@@ -662,18 +665,18 @@ def attention(qkv: torch.Tensor, lane, ctx, out: torch.Tensor, nq: int, nkv: int
         fork, join = _side_events(qkv.device)
         fork.record(main)
         side.wait_event(fork)
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights)
         with torch.cuda.stream(side):
             attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first)
+                             plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights)
             join.record(side)
         main.wait_event(join)
         return out
     if plan["n_decode"]:
         attention_decode(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["decode_rows"], plan["n_decode"],
-                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first)
+                         plan["max_kv_len"], plan.get("work"), plan.get("work_slots", 0), keep_first, wide_weights)
     if plan["tiles"] is not None:
-        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first)
+        attention_prefill(qkv, lane, ctx, out, nq, nkv, head_dim, scale, window, plan["tiles"], plan.get("tiles_tc"), keep_first, wide_weights)
     return out
 
 
@@ -815,7 +818,7 @@ def linear_scan(rec: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, 
     b_ptr = base + 4 * (off_v + heads * v_dim + heads) if gated else None
     lib.call("ns_linear_scan", base, base + 4 * kv_heads * dp, base + 4 * off_v, g_ptr, b_ptr, None if gated else decay.data_ptr(),
              rec.stride(0), state.data_ptr(), state.stride(0), ctx.qo_indptr.data_ptr(), ctx.state_slot.data_ptr(), out.data_ptr(),
-             out.stride(0), ctx.n_requests, heads, kv_heads, head_dim, v_dim, _stream())
+             out.stride(0), ctx.n_requests, heads, kv_heads, head_dim, v_dim, int(ctx.max_q_len or 1), sm_count(), _stream())
     return out
 
 

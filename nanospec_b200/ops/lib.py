@@ -35,7 +35,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_qk_norm_rope_store": [_P, _I, _P, _P, _P, _I, _P, _F, _I, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ns_delta_prepare": [_P, _I, _P, _I, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "ns_rotary_prepare": [_P, _I, _P, _P, _P, _F, _I, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
-    "ns_linear_scan": [_P, _P, _P, _P, _P, _P, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ns_linear_scan": [_P, _P, _P, _P, _P, _P, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ns_head_norm_gate": [_P, _I, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P],
     "ns_sample_rows": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "ns_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
@@ -50,8 +50,8 @@ _SIGNATURES: dict[str, list] = {
     "ns_gemm_bf16_tc_gated": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ns_attention_prefill_tc": [_P, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "ns_wait_probe": [_P, _L, _P, _P],
-    "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
-    "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
+    "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "ns_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
 }
 
@@ -93,13 +93,46 @@ def launch_count() -> int:
     return _launches
 
 
+_timed: list | None = None  # (entry point, start event, end event) of every call while kernel timing is on
+
+
+def start_kernel_timing() -> None:
+    """From now on every entry point's launches are bracketed by CUDA events on the current stream (measurement only:
+    the events keep neighbouring kernels from overlapping, and nothing may be captured into a graph meanwhile)."""
+    global _timed
+    _timed = []
+
+
+def stop_kernel_timing() -> dict[str, tuple[int, float]]:
+    """Ends kernel timing: entry point -> (calls, milliseconds on the device in total)."""
+    global _timed
+    import torch
+
+    rows, _timed = _timed or [], None
+    torch.cuda.synchronize()
+    out: dict[str, tuple[int, float]] = {}
+    for name, a, b in rows:
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + a.elapsed_time(b))
+    return out
+
+
 def call(name: str, *args) -> None:
     global _launches
     lib = load()
     fn = getattr(lib, name, None)
     if fn is None:
         raise KernelError(f"the native library {_path} has no entry point {name}; rebuild it")
-    status = fn(*args)
+    if _timed is not None:
+        import torch
+
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        status = fn(*args)
+        b.record()
+        _timed.append((name, a, b))
+    else:
+        status = fn(*args)
     _launches += 1
     if status != 0:
         raise KernelError(f"{name} failed with status {status}: {lib.ns_last_error().decode(errors='replace')}")

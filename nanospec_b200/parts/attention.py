@@ -32,6 +32,7 @@ class GQAAttention(Part):
     keep_first   with a window: the first so many keys of a sequence stay visible to every later query
     qk_norm      {"eps": e}: an RMS norm over the whole q projection and one over the whole k projection (one statistic
                  over all heads, gains `q_norm` / `k_norm` of the projections' sizes), before the rotation
+    wide_weights True: the softmax weights keep about 16 bits where they meet the values (`ops.attention`)
     names        the tensors' names after the part's prefix, keys "q", "k", "v", "o", "q_norm", "k_norm"
                  (default the Hugging Face ones)."""
 
@@ -49,6 +50,7 @@ class GQAAttention(Part):
         self.v_dim = int(p.get("v_dim") or self.head_dim)
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
         self.qk_norm = dict(p["qk_norm"]) if p.get("qk_norm") else None
+        self.wide_weights = bool(p.get("wide_weights"))
         names = dict(p.get("names") or {})
         self.names = {k: names.get(k, d) for k, d in (("q", "q_proj.weight"), ("k", "k_proj.weight"), ("v", "v_proj.weight"),
                                                       ("o", "o_proj.weight"), ("q_norm", "q_norm.weight"), ("k_norm", "k_norm.weight"))}
@@ -109,7 +111,7 @@ class GQAAttention(Part):
                                            q_gain=self.q_gain, k_gain=self.k_gain, eps=float(qn["eps"]) if qn else 0.0)
             attn = ctx.buffer("attn_out", self.o_in)
             ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window,
-                          self.keep_first, self.v_dim)
+                          self.keep_first, self.v_dim, self.wide_weights)
             return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)
         fused = getattr(self.position, "project_rotate_store", None)
         if fused is None or not fused(x, self.w_qkv, qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim, writes):
@@ -119,5 +121,6 @@ class GQAAttention(Part):
             elif writes:
                 ops.kv_store(qkv, ctx, lane, self.heads, self.kv_heads, self.head_dim)
         attn = ctx.buffer("attn_out", self.q_size)
-        ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window, self.keep_first)
+        ops.attention(qkv, lane, ctx, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window, self.keep_first,
+                      wide_weights=self.wide_weights)
         return ops.linear(attn, self.w_o, ctx.buffer("branch", self.hidden), sink=sink)

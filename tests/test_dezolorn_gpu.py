@@ -159,6 +159,17 @@ def test_layernorm_and_rotation_kernels():
     out = torch.empty(5, 100, device="cuda")
     ops.add_layernorm(resid, None, gain.cuda(), 1e-3, out)
     assert (out.cpu() - plain.layer_norm(x.double(), gain.double(), 1e-3).float()).abs().max() < 1e-5
+    for width in (1024, 2048 + 8, 4096):  # the widths that take the kernel with the row in registers, with a branch to add
+        x, br, gain = torch.randn(7, width, generator=g) * 2 - 1, torch.randn(7, width, generator=g).bfloat16(), torch.randn(width, generator=g)
+        resid, out = x.cuda().clone(), torch.empty(7, width, device="cuda", dtype=torch.bfloat16)
+        ops.add_layernorm(resid, br.cuda(), gain.cuda(), 1e-6, out)
+        want = plain.layer_norm(x.double() + br.double(), gain.double(), 1e-6)
+        assert (resid.cpu().double() - (x.double() + br.double())).abs().max() < 1e-6
+        assert (out.cpu().double() - want).abs().max() < 0.02 * want.abs().max()
+        rows = torch.tensor([5, 0, 3], dtype=torch.int32, device="cuda")
+        picked = torch.empty(3, width, device="cuda")
+        ops.add_layernorm(resid, None, gain.cuda(), 1e-6, picked, rows=rows)
+        assert (picked.cpu().double() - want[[5, 0, 3]]).abs().max() < 1e-4
     for rot in ({"dims": 12, "base": 100.0}, {"dims": 16, "base": 50000.0, "scaling": {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0}}):
         f, mag = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
         f_want, mag_want = plain.rotary_frequencies(rot)
