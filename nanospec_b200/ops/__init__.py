@@ -801,13 +801,15 @@ def rotary_prepare(proj: torch.Tensor, ctx, inv_freq: torch.Tensor | None, magni
 
 def linear_scan(rec: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, v_dim: int,
                 decay: torch.Tensor | None = None, gated: bool = False) -> torch.Tensor:
-    """The recurrence over each request's tokens of this step (csrc/recurrent.cu).  `rec` rows: [q: kv_heads*Dp | k: kv_heads*Dp |
-    v: heads*v_dim] and, when `gated` (the delta rule), [g: heads | beta: heads] after them; otherwise `decay` [heads] float32.
+    """The recurrence over each request's tokens of this step (csrc/recurrent.cu).  `rec` rows, as the preparation kernels write
+    them: [q: kv_heads*Dp | k: kv_heads*Dp | v: heads*v_dim], then, when `gated` (the delta rule), [g: heads | beta: heads], then
+    [k . q: kv_heads]; without `gated`, `decay` [heads] float32.
     `state` [slots, floats] holds S [heads, head_dim, v_dim] at the start of each slot's row; `out` [N, heads*v_dim] float32."""
     _cuda(rec, state, out, decay)
     dp = scan_padded_dim(head_dim)
     off_v = 2 * kv_heads * dp
-    need = off_v + heads * v_dim + (2 * heads if gated else 0)
+    off_kq = off_v + heads * v_dim + (2 * heads if gated else 0)
+    need = off_kq + kv_heads
     if rec.dtype != torch.float32 or out.dtype != torch.float32 or state.dtype != torch.float32 or rec.shape[1] < need \
             or rec.stride(1) != 1 or out.stride(1) != 1 or not state.is_contiguous() or state.shape[1] < heads * head_dim * v_dim:
         raise KernelError("linear_scan: float32 operands of the sizes the heads need")
@@ -816,7 +818,8 @@ def linear_scan(rec: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, 
     base = rec.data_ptr()
     g_ptr = base + 4 * (off_v + heads * v_dim) if gated else None
     b_ptr = base + 4 * (off_v + heads * v_dim + heads) if gated else None
-    lib.call("ns_linear_scan", base, base + 4 * kv_heads * dp, base + 4 * off_v, g_ptr, b_ptr, None if gated else decay.data_ptr(),
+    lib.call("ns_linear_scan", base, base + 4 * kv_heads * dp, base + 4 * off_v, g_ptr, b_ptr, base + 4 * off_kq,
+             None if gated else decay.data_ptr(),
              rec.stride(0), state.data_ptr(), state.stride(0), ctx.qo_indptr.data_ptr(), ctx.state_slot.data_ptr(), out.data_ptr(),
              out.stride(0), ctx.n_requests, heads, kv_heads, head_dim, v_dim, int(ctx.max_q_len or 1), sm_count(), _stream())
     return out

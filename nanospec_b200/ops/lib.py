@@ -35,7 +35,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_qk_norm_rope_store": [_P, _I, _P, _P, _P, _I, _P, _F, _I, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ns_delta_prepare": [_P, _I, _P, _I, _P, _P, _P, _L, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "ns_rotary_prepare": [_P, _I, _P, _P, _P, _F, _I, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
-    "ns_linear_scan": [_P, _P, _P, _P, _P, _P, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ns_linear_scan": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ns_head_norm_gate": [_P, _I, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P],
     "ns_sample_rows": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "ns_attention_decode": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],

@@ -53,7 +53,7 @@ class Retention(Part):
         self.names = {k: names.get(k, k + "_proj.weight") for k in ("q", "k", "v", "g", "o")}
         self.qk_size, self.v_size = self.heads * self.head_dim, self.heads * self.v_dim
         self.dp = ops.scan_padded_dim(self.head_dim)
-        self.rec_cols = -(-(2 * self.heads * self.dp + self.v_size) // 4) * 4
+        self.rec_cols = -(-(2 * self.heads * self.dp + self.v_size + self.heads) // 4) * 4  # q, k, v, k . q
         self.w_in: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
 
@@ -116,7 +116,7 @@ class GatedDeltaRule(Part):
         self.qk_size, self.v_size = self.kv_heads * self.head_dim, self.heads * self.v_dim
         self.channels = 2 * self.qk_size + self.v_size
         self.dp = ops.scan_padded_dim(self.head_dim)
-        self.rec_cols = -(-(2 * self.kv_heads * self.dp + self.v_size + 2 * self.heads) // 4) * 4
+        self.rec_cols = -(-(2 * self.kv_heads * self.dp + self.v_size + 2 * self.heads + self.kv_heads) // 4) * 4  # q, k, v, g, beta, k . q
         self.s_floats = self.heads * self.head_dim * self.v_dim
         self.off_g = self.channels
         self.off_b = self.channels + self.v_size

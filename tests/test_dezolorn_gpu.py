@@ -317,3 +317,28 @@ def test_greedy_generation_through_the_engine(dtype, graphs, tmp_path):
             row = z[len(p) + j - 1]
             gap = float(row.max() - row[tok])
             assert gap <= (1e-3 if dtype == torch.float32 else 0.3), f"token {j}: the oracle prefers another by {gap}"
+
+
+def test_command_line_and_sampling(tmp_path):
+    """The package's command line on a Dezolorn folder: random weights from a config.json, then generation with
+    temperature, top-k and top-p under fixed seeds (twice the same), and greedy generation."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(mixed_config()))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "nanospec_b200", *a], cwd=root, capture_output=True, text=True, timeout=600)
+    r = run("random-weights", "--config", str(cfg_path), "--out", str(tmp_path / "model"), "--seed", "4")
+    assert r.returncode == 0, r.stderr
+    outs = []
+    for _ in range(2):
+        r = run("generate", "--model", str(tmp_path / "model"), "--prompt-lens", "5", "21", "--max-tokens", "9", "--temperature", "0.8",
+                "--top-k", "20", "--top-p", "0.9", "--seed", "3", "--ignore-eos")
+        assert r.returncode == 0, r.stderr
+        outs.append([json.loads(line)["output_ids"] for line in r.stdout.splitlines() if '"output_ids"' in line])
+    assert outs[0] == outs[1] and [len(o) for o in outs[0]] == [9, 9]
+    r = run("generate", "--model", str(tmp_path / "model"), "--dtype", "float32", "--prompt-ids", "1 2 3 4", "--max-tokens", "6", "--ignore-eos")
+    assert r.returncode == 0, r.stderr
+    assert len(json.loads(r.stdout.splitlines()[0])["output_ids"]) == 6
