@@ -205,18 +205,20 @@ __device__ __forceinline__ float sum_parts(float v) {  // over the LPC lanes of 
     return v;
 }
 
-template <int R, int LPC, int C>
+template <int R, int LPC, int C, bool ONE>
 struct ScanShape {
     static constexpr int kCols = C * 128 / LPC;             // columns per block
     static constexpr int kDp = R * LPC;
-    static constexpr int kTokens = kDp > 128 ? 8 : 16;      // tokens per stage
+    // tokens per stage; ONE: a step in which every request brings one token keeps its blocks small, so that many of them
+    // fit an SM and the state, which is all that such a step moves, streams at full rate
+    static constexpr int kTokens = ONE ? 1 : (kDp > 128 ? 8 : 16);
     static constexpr int kSeg = R + 4, kRow = LPC * kSeg;   // a staged row of q or k
     static constexpr int kStage = kTokens * (2 * kRow + kCols + 4);  // floats: q rows, k rows, v slices, gates, betas, k . q
     static constexpr size_t kBytes = 2 * (size_t)kStage * sizeof(float);
 };
 
 // C columns per lane (their sums are independent of one another); the launcher uses 1.
-template <int R, int LPC, int C>
+template <int R, int LPC, int C, bool ONE>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                    const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ kq,
@@ -225,7 +227,7 @@ linear_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, con
                    int H, int G, int D, int V) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
-    using Sh = ScanShape<R, LPC, C>;
+    using Sh = ScanShape<R, LPC, C, ONE>;
     constexpr int CW = 32 / LPC;       // columns per warp and turn
     constexpr int CB = 128 / LPC;      // columns per block and turn
     extern __shared__ __align__(16) float scan_smem[];
@@ -289,7 +291,7 @@ linear_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, con
         const int n0 = start + ch * Sh::kTokens, cnt = min(Sh::kTokens, end - n0);
         // the operands of the next token are read from shared memory while this one's sums travel through the shuffles
         // (the widest heads would not keep two tokens' operands in registers)
-        constexpr bool kAhead = R <= 32;
+        constexpr bool kAhead = R <= 32 && !ONE;
         constexpr int RN = kAhead ? R : 4;
         float kn[RN], qn[RN];
         if (kAhead) {
@@ -431,22 +433,33 @@ NS_API int ns_linear_scan_rows(int D) {
 }
 
 namespace {
-template <int R, int LPC, int C>
-int launch_scan(const float* q, const float* k, const float* v, const float* gate, const float* beta, const float* kq,
+template <int R, int LPC, int C, bool ONE>
+int launch_scan_as(const float* q, const float* k, const float* v, const float* gate, const float* beta, const float* kq,
                 const float* decay, int ld, float* state, long long state_floats, const int* qo_indptr, const int* state_slot, float* out, int ld_out,
                 int n_requests, int H, int G, int D, int V, cudaStream_t stream) {
-    using Sh = ScanShape<R, LPC, C>;
+    using Sh = ScanShape<R, LPC, C, ONE>;
     static bool configured = false;
     if (!configured && Sh::kBytes > 48 * 1024) {
-        NS_CUDA(cudaFuncSetAttribute(linear_scan_kernel<R, LPC, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::kBytes));
+        NS_CUDA(cudaFuncSetAttribute(linear_scan_kernel<R, LPC, C, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::kBytes));
         configured = true;
     }
     const int col_blocks = (V + Sh::kCols - 1) / Sh::kCols;
     if (H > 65535 || col_blocks > 65535) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_linear_scan: %d heads of %d columns exceed the grid", H, V);
-    NS_LAUNCH((linear_scan_kernel<R, LPC, C>), dim3(n_requests, H, col_blocks), 128, Sh::kBytes, stream, q, k, v, gate, beta, kq, decay, ld,
+    NS_LAUNCH((linear_scan_kernel<R, LPC, C, ONE>), dim3(n_requests, H, col_blocks), 128, Sh::kBytes, stream, q, k, v, gate, beta, kq, decay, ld,
               state, state_floats, qo_indptr, state_slot, out, ld_out, H, G, D, V);
     NS_CHECK_LAUNCH("ns_linear_scan");
     return NS_OK;
+}
+
+template <int R, int LPC, int C>
+int launch_scan(const float* q, const float* k, const float* v, const float* gate, const float* beta, const float* kq,
+                const float* decay, int ld, float* state, long long state_floats, const int* qo_indptr, const int* state_slot,
+                float* out, int ld_out, int n_requests, int H, int G, int D, int V, cudaStream_t stream, int longest) {
+    if (longest <= 1)
+        return launch_scan_as<R, LPC, C, true>(q, k, v, gate, beta, kq, decay, ld, state, state_floats, qo_indptr, state_slot, out,
+                                               ld_out, n_requests, H, G, D, V, stream);
+    return launch_scan_as<R, LPC, C, false>(q, k, v, gate, beta, kq, decay, ld, state, state_floats, qo_indptr, state_slot, out,
+                                            ld_out, n_requests, H, G, D, V, stream);
 }
 }  // namespace
 
@@ -476,7 +489,7 @@ NS_API int ns_linear_scan(const float* q, const float* k, const float* v, const 
     const long long blocks4 = (long long)n_requests * H * ((V + 31) / 32);
     const int sms = n_sms > 0 ? n_sms : 148;
     const int lanes = g_scan_lanes == 4 || g_scan_lanes == 8 ? g_scan_lanes : (longest >= 64 && R4 >= 8 && blocks4 < 4ll * sms ? 8 : 4);
-#define NS_SCAN_ARGS q, k, v, gate, beta, kq, decay, ld, state, state_floats, qo_indptr, state_slot, out, ld_out, n_requests, H, G, D, V, stream
+#define NS_SCAN_ARGS q, k, v, gate, beta, kq, decay, ld, state, state_floats, qo_indptr, state_slot, out, ld_out, n_requests, H, G, D, V, stream, longest
     switch (R4) {
         case 4: return launch_scan<4, 4, 1>(NS_SCAN_ARGS);
         case 8: return lanes == 8 ? launch_scan<4, 8, 1>(NS_SCAN_ARGS) : launch_scan<8, 4, 1>(NS_SCAN_ARGS);

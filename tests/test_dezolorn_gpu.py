@@ -133,6 +133,8 @@ SINGLE = {
     "delta, one tap, equal heads": lambda: config([delta_layer(heads=2, kv_heads=2, dim=5, vdim=7, conv=1)]),
     "delta, five taps, wide head": lambda: config([delta_layer(heads=3, kv_heads=1, dim=72, vdim=36, conv=5)]),
     "feed-forward and no soft cap": lambda: config([delta_layer(ff=30)], logit_scale=1.0, softcap=0.0),
+    "a width and a feed-forward that are no multiples of 8": lambda: config(
+        [attention_layer(ff=30), retention_layer(ff=77), delta_layer()], width=50, vocab=101),
 }
 
 
