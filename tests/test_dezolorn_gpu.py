@@ -112,11 +112,23 @@ def run_cut(runner, req_id, ids, cuts):
 
 
 def close(got, want, dtype, what=""):
-    """float32: a few float32 roundings of logits of size ~ the cap; bfloat16: the roundings of a bfloat16 pipeline."""
+    """float32: a few float32 roundings, relative to the size of the logits, at every position.  bfloat16: the roundings of a
+    bfloat16 pipeline, which grow with the depth of the model and stand out where a read-out nearly cancels before its norm:
+    the error of a position (root mean square over the vocabulary, the mean taken off) is set against the spread of the
+    logits - small at the median position, moderate at nine in ten, never of the logits' own size, which is what a lost
+    state, a wrong window or a wrong slot gives."""
     want = want.float()
-    err = (got - want).abs().max().item()
-    lim = 2e-4 if dtype == torch.float32 else 0.25
-    assert err <= lim, f"{what}: largest difference {err} (limit {lim})"
+    if dtype == torch.float32:
+        err = (got - want).abs().amax(-1)
+        lim = 1e-4 * max(5.0, float(want.abs().max()))
+        assert err.max() <= lim, f"{what}: largest difference {float(err.max())} at position {int(err.argmax())} (limit {lim})"
+        return
+    d = got - want
+    ratio = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / want.std()
+    q = ratio.sort().values
+    median, most, worst = float(q[len(q) // 2]), float(q[int(0.9 * (len(q) - 1))]), float(q[-1])
+    assert (median <= 0.05 or len(q) < 8) and most <= 0.2 and worst <= 0.5, \
+        f"{what}: error over spread {median:.3f} at the median position, {most:.3f} at nine in ten, {worst:.3f} at the worst (limits 0.05, 0.2, 0.5)"
 
 
 # ---- every mixer alone, and their parts -------------------------------------------------------------------------------
@@ -237,14 +249,46 @@ def test_far_tokens_reach_through_the_state(dtype, tmp_path):
 
 # ---- batches, reuse of pages and slots, long decoding -----------------------------------------------------------------
 
+def drawn_config(seed: int) -> dict:
+    """A configuration drawn from a seed: layer kinds in any order, every size from a short list, a span that runs one to
+    three times anywhere in the stack."""
+    import random
+
+    r = random.Random(seed)
+    pick = r.choice
+    layers = []
+    for _ in range(r.randint(3, 6)):
+        kind = pick(["attention", "retention", "delta"])
+        ff = pick([None, 24, 64, 100])
+        if kind == "attention":
+            kv = pick([1, 2, 3])
+            dim = pick([8, 16, 32, 40, 64])
+            layers.append(attention_layer(heads=kv * pick([1, 2, 4]), kv_heads=kv, dim=dim, vdim=pick([dim, dim, 8, 24]), size=pick([1, 3, 16, 33, 500]),
+                                          keep=pick([0, 1, 4, 9, 40]), dims=pick([dim, dim // 2 // 2 * 2, 2]), scaling=pick([True, False]), ff=ff))
+        elif kind == "retention":
+            h = pick([1, 2, 5])
+            dim = pick([4, 12, 32, 64, 68])
+            layers.append(retention_layer(heads=h, dim=dim, vdim=pick([4, 10, 32, 48]), dims=pick([dim, 4, 0]),
+                                          decay=[1 - 2.0 ** -r.randint(1, 9) for _ in range(h)], ff=ff))
+        else:
+            kv = pick([1, 2])
+            layers.append(delta_layer(heads=kv * pick([1, 2, 3]), kv_heads=kv, dim=pick([4, 16, 20, 64]), vdim=pick([4, 16, 40]),
+                                      conv=pick([1, 2, 4, 6]), ff=ff))
+    start = r.randint(0, len(layers) - 1)
+    stop = r.randint(start, len(layers))
+    return config(layers, width=pick([40, 64, 72, 136]), vocab=pick([64, 97, 300]), loop={"start": start, "stop": stop, "times": r.randint(1, 3)},
+                  logit_scale=pick([1.0, 0.25, 2.0]), softcap=pick([0.0, 5.0, 30.0]), eps=pick([1e-5, 1e-6]))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_unequal_batches_and_reuse(dtype, tmp_path):
+@pytest.mark.parametrize("which", ["mixed", 1, 2, 3, 4, 5, 6])
+def test_unequal_batches_and_reuse(which, dtype, tmp_path):
     """Four requests of unequal length share steps - portions beside single tokens - on a pool that only their peak
     fits; requests end and others take their pages and state slots.  Every position against the oracle, which is each
-    request alone."""
+    request alone.  Once on the configuration with all three mixers, then on configurations drawn from seeds."""
     from nanospec_b200.engine.step import StepEntry
 
-    cfg = mixed_config()
+    cfg = mixed_config() if which == "mixed" else drawn_config(which)
     runner, w = make(tmp_path, cfg, seed=31, dtype=dtype, blocks=30, page=4, slots=3)
     seqs = {i: tokens(n, cfg["vocab"], 40 + i) for i, n in enumerate([37, 2, 19, 50, 1, 23])}
     want = {i: plain.forward(cfg, w, s) for i, s in seqs.items()}
