@@ -278,6 +278,94 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, int row_stride, const int* __rest
         slot = (size_t)page * nkv * page_size + (size_t)(pos % page_size);  // + kv head * page_size
     }
     const float fpos = (float)pos;
+    // 16-byte accesses: eight features at a time, when heads, the rotated part and the rows allow it
+    const bool vec = d % 8 == 0 && (2 * rot_pairs) % 8 == 0 && (interleaved || rot_pairs % 8 == 0) && row_stride % 8 == 0 &&
+                     (uintptr_t)qkv % 16 == 0 && (!write_kv || (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0 && dv % 8 == 0)) &&
+                     (!q_gain || (uintptr_t)q_gain % 16 == 0) && (!k_gain || (uintptr_t)k_gain % 16 == 0);
+    if (vec) {
+        // per head: the rotated part in pieces of 8 features (interleaved) or of 8 pairs (two pieces half the part apart), then the rest
+        const int rot_items = interleaved ? rot_pairs / 4 : rot_pairs / 8;
+        const int items = rot_items + (d - 2 * rot_pairs) / 8;
+        for (int w = threadIdx.x; w < (nq + nkv) * items; w += blockDim.x) {
+            const int h = w / items, it = w - h * items;
+            const bool is_k = h >= nq;
+            const int base = h * d;
+            const float* gain = is_k ? k_gain : q_gain;
+            const int goff = is_k ? base - q_size : base;
+            const float inv = is_k ? inv_k : inv_q;
+            T* kc = (is_k && write_kv) ? k_cache + (slot + (size_t)(h - nq) * page_size) * d : nullptr;
+            if (it >= rot_items) {  // features that pass
+                const int e = 2 * rot_pairs + (it - rot_items) * 8;
+                float x[8];
+                ld8(row + base + e, x);
+                if (gain) {
+                    float g[8];
+                    ld8(gain + goff + e, g);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * g[i];
+                    st8(row + base + e, x);
+                }
+                if (kc) st8(kc + e, x);
+            } else if (interleaved) {
+                const int e = it * 8;
+                float x[8];
+                ld8(row + base + e, x);
+                if (gain) {
+                    float g[8];
+                    ld8(gain + goff + e, g);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * g[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float sn, cs;
+                    sincosf(fpos * inv_freq[it * 4 + i], &sn, &cs);
+                    sn *= magnitude; cs *= magnitude;
+                    const float a = x[2 * i], b = x[2 * i + 1];
+                    x[2 * i] = a * cs - b * sn;
+                    x[2 * i + 1] = b * cs + a * sn;
+                }
+                st8(row + base + e, x);
+                if (kc) st8(kc + e, x);
+            } else {
+                const int e = it * 8;
+                float lo[8], hi[8];
+                ld8(row + base + e, lo);
+                ld8(row + base + e + rot_pairs, hi);
+                if (gain) {
+                    float g[8];
+                    ld8(gain + goff + e, g);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) lo[i] = lo[i] * inv * g[i];
+                    ld8(gain + goff + e + rot_pairs, g);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) hi[i] = hi[i] * inv * g[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float sn, cs;
+                    sincosf(fpos * inv_freq[e + i], &sn, &cs);
+                    sn *= magnitude; cs *= magnitude;
+                    const float a = lo[i], b = hi[i];
+                    lo[i] = a * cs - b * sn;
+                    hi[i] = b * cs + a * sn;
+                }
+                st8(row + base + e, lo);
+                st8(row + base + e + rot_pairs, hi);
+                if (kc) { st8(kc + e, lo); st8(kc + e + rot_pairs, hi); }
+            }
+        }
+        if (write_kv) {
+            const T* v = row + q_size + k_size;
+            for (int w = threadIdx.x; w < nkv * dv / 8; w += blockDim.x) {
+                const int h = (w * 8) / dv, e = w * 8 - h * dv;
+                float x[8];
+                ld8(v + w * 8, x);
+                st8(v_cache + (slot + (size_t)h * page_size) * dv + e, x);
+            }
+        }
+        return;
+    }
     const int units = rot_pairs + (d - 2 * rot_pairs);  // per head: the pairs, then the features that pass
     for (int w = threadIdx.x; w < (nq + nkv) * units; w += blockDim.x) {
         const int h = w / units, u = w - h * units;
