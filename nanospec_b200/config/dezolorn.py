@@ -65,6 +65,10 @@ class DezolornConfig:
             if kind not in MIXER_TYPES:
                 raise ConfigError(f"Dezolorn config: {where} has the unknown mixer type {kind!r} (known: {', '.join(MIXER_TYPES)})")
             m = dict(_need(entry, "mixer", where))
+            if m.get("heads") is not None and m.get("kv_heads") is None and kind != "retention":
+                m["kv_heads"] = m["heads"]      # a file that leaves it out means one key head per head
+            if m.get("dim") is not None and m.get("vdim") is None:
+                m["vdim"] = m["dim"]            # ... and values as wide as keys
             for key in {"attention": ("heads", "kv_heads", "dim", "vdim", "scale", "mask", "rot"),
                         "retention": ("heads", "dim", "vdim", "decay", "rot"),
                         "delta": ("heads", "kv_heads", "dim", "vdim", "conv")}[kind]:
