@@ -436,7 +436,7 @@ DESIGN_SIZES = {
     "w2048": dict(width=2048, ff=8192, heads=32, kv_heads=8, dim=64, s_heads=16, s_kv=8, s_dim=128, s_vdim=128, layers=8),
     "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, s_heads=32, s_kv=16, s_dim=128, s_vdim=128, layers=4),
 }
-DESIGN_VOCAB, DESIGN_WINDOW, DESIGN_KEEP = 32768, 1024, 4
+DESIGN_VOCAB, DESIGN_WINDOW, DESIGN_KEEP = 32768, 1024, 8
 FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12  # CUDA cores: 148 SMs x 128 lanes x 2 flops x the top clock
 
 
@@ -444,7 +444,7 @@ def dezolorn_config(sz: dict) -> dict:
     attention = {"type": "attention", "mlp": {"kind": "dense", "ff": sz["ff"]}, "mixer": {
         "heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
         "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP},
-        "rot": {"dims": sz["dim"], "base": 500000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+        "rot": {"dims": sz["dim"], "base": 1000000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}}
     retention = {"type": "retention", "mlp": {"kind": "dense", "ff": sz["ff"]}, "mixer": {
         "heads": sz["s_heads"], "dim": sz["s_dim"], "vdim": sz["s_vdim"],
         "decay": [1.0 - 2.0 ** -(5 + h % 8) for h in range(sz["s_heads"])], "rot": {"dims": sz["s_dim"], "base": 10000.0}}}
@@ -453,7 +453,7 @@ def dezolorn_config(sz: dict) -> dict:
     pattern = [attention, retention, delta, attention]
     return {"architecture": "Dezolorn", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6},
             "layers": [pattern[i % 4] for i in range(sz["layers"])], "loop": {"start": 0, "stop": 0, "times": 1},
-            "logit_scale": 1.0, "logit_softcap": 30.0}
+            "logit_scale": 1.0, "logit_softcap": 20.0}
 
 
 def llama_sibling(sz: dict):

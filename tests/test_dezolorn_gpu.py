@@ -277,7 +277,7 @@ def drawn_config(seed: int) -> dict:
     start = r.randint(0, len(layers) - 1)
     stop = r.randint(start, len(layers))
     return config(layers, width=pick([40, 64, 72, 136]), vocab=pick([64, 97, 300]), loop={"start": start, "stop": stop, "times": r.randint(1, 3)},
-                  logit_scale=pick([1.0, 0.25, 2.0]), softcap=pick([0.0, 5.0, 30.0]), eps=pick([1e-5, 1e-6]))
+                  logit_scale=pick([1.0, 0.5, 2.0]), softcap=pick([0.0, 5.0, 20.0]), eps=pick([1e-5, 1e-6]))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
