@@ -1,3 +1,3 @@
-from . import dezolorn, llama  # registers Dezolorn and LlamaForCausalLM
+from . import dezolorn, llama, sorizen  # registers Dezolorn, LlamaForCausalLM and Sorizen
 
-__all__ = ["dezolorn", "llama"]
+__all__ = ["dezolorn", "llama", "sorizen"]

@@ -25,6 +25,9 @@ class CacheStorage:
             if s.v_dim is None:
                 self.group_kv.append(torch.zeros((len(s.lanes), 2, manager.num_blocks, s.kv_heads, s.page_size, s.head_dim),
                                                  dtype=dtype, device=device))
+            elif s.v_dim == 0:  # no values of their own (a latent that is key and value at once): the keys' tensor alone
+                self.group_kv.append((torch.zeros((len(s.lanes), manager.num_blocks, s.kv_heads, s.page_size, s.head_dim),
+                                                  dtype=dtype, device=device), None))
             else:  # values of another width than the keys: a tensor each, [lane in group, page, kv head, offset, dim]
                 self.group_kv.append(tuple(
                     torch.zeros((len(s.lanes), manager.num_blocks, s.kv_heads, s.page_size, d), dtype=dtype, device=device)
@@ -37,7 +40,7 @@ class CacheStorage:
         self.lane_needs = lane_needs
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for g in self.group_kv for t in (g if isinstance(g, tuple) else (g,))) + \
+        return sum(t.numel() * t.element_size() for g in self.group_kv for t in (g if isinstance(g, tuple) else (g,)) if t is not None) + \
             sum(t.numel() * t.element_size() for t in self.state.values())
 
     def lane_views(self, group_tables: list[torch.Tensor | None]) -> list[LaneView]:
@@ -51,7 +54,7 @@ class CacheStorage:
             spec = self.manager.groups[gi].spec
             idx = spec.lanes.index(lane)
             store = self.group_kv[gi]
-            kv = (store[0][idx], store[1][idx]) if isinstance(store, tuple) else store[idx]
+            kv = (store[0][idx], None if store[1] is None else store[1][idx]) if isinstance(store, tuple) else store[idx]
             views.append(LaneView(kv[0], kv[1], group_tables[gi], spec.page_size, spec.window, self.state.get(lane)))
         return views
 

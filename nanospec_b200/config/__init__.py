@@ -1,5 +1,6 @@
 from .files import ConfigError, read_config_files
 from .dezolorn import DezolornConfig
+from .sorizen import SorizenConfig
 from .llama import Llama3RopeScaling, LlamaConfig
 from .recipe import LayerSpec, ModelRecipe, PartSpec, Run
 from .registry import Architecture, register_architecture, registered_architectures, resolve_architecture
@@ -7,6 +8,6 @@ from .engine import EngineConfig
 
 __all__ = [
     "Architecture", "ConfigError", "DezolornConfig", "EngineConfig", "LayerSpec", "Llama3RopeScaling", "LlamaConfig",
-    "ModelRecipe", "PartSpec", "Run", "read_config_files", "register_architecture",
+    "ModelRecipe", "PartSpec", "Run", "SorizenConfig", "read_config_files", "register_architecture",
     "registered_architectures", "resolve_architecture",
 ]

@@ -33,7 +33,8 @@ class LayerSpec:
 
     `prefix` is the layer's part of every tensor name ("model.layers.3."); `names` maps
     the arrangement's slots ("mixer", "feed_forward", "norm_mixer", "norm_feed_forward")
-    to the sub-prefix used in the checkpoint ("self_attn.", "input_layernorm.", ...).
+    to the sub-prefix used in the checkpoint ("self_attn.", "input_layernorm.", ...).  `params` holds the
+    arrangement's own constants (how many copies of the stream it keeps, say).
     """
 
     block: str
@@ -42,9 +43,11 @@ class LayerSpec:
     feed_forward: PartSpec | None  # None: the layer has no feed-forward sublayer
     norm: PartSpec
     names: Mapping[str, str]
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "names", MappingProxyType(dict(self.names)))
+        object.__setattr__(self, "params", MappingProxyType(dict(self.params)))
 
 
 @dataclass(frozen=True)

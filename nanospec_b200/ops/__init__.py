@@ -835,3 +835,183 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor | None, gain: torch.Tenso
     lib.call("ns_head_norm_gate", o.data_ptr(), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(gain), float(eps),
              out.data_ptr(), out.stride(0), ctx.token_req.data_ptr(), o.shape[0], heads, v_dim, dtype_code(out.dtype), _stream())
     return out
+
+
+# ---- a stream in several copies, a cached latent, routed experts ------------------------------------------------------
+
+def embed_streams(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+    """out[n, s * hidden + h] = float(table[ids[n], h]) * scale for each of the `copies` streams."""
+    _cuda(table, ids, out)
+    _i32(ids, "ids")
+    n, hidden = out.shape[0], table.shape[1]
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous() or out.shape[1] != copies * hidden \
+            or ids.numel() != n:
+        raise KernelError(f"embed_streams: table {tuple(table.shape)}, ids {ids.numel()}, out {tuple(out.shape)}, {copies} copies do not agree")
+    lib.call("ns_embed_streams", table.data_ptr(), ids.data_ptr(), out.data_ptr(), n, hidden, table.shape[0], float(scale),
+             int(copies), dtype_code(table.dtype), _stream())
+    return out
+
+
+def stream_mix_norm(streams: torch.Tensor, n_streams: int, pending: torch.Tensor | None, mix: torch.Tensor | None,
+                    out_w: torch.Tensor | None, in_w: torch.Tensor | None, gain: torch.Tensor | None, bias: torch.Tensor | None,
+                    eps: float, centered: bool, out: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """One pass over each row of `streams` [N, n_streams * H] (float32): the streams take the pending branch
+    (x_t = sum_s mix[s, t] x_s + out_w[t] * pending; identity coefficients when None), in place unless `rows` selects
+    rows; then out = norm(sum_s in_w[s] x_s) (every stream once when `in_w` is None) with `gain`, optional `bias`,
+    RMS or `centered`.  `out` None: only the streams are updated."""
+    _cuda(streams, pending, mix, out_w, in_w, gain, bias, out, rows)
+    _i32(rows, "rows")
+    hidden = streams.shape[1] // n_streams
+    if streams.dtype != torch.float32 or not streams.is_contiguous() or streams.shape[1] != n_streams * hidden:
+        raise KernelError("stream_mix_norm: the streams are contiguous float32 rows of n_streams * hidden")
+    for t, size, name in ((mix, n_streams * n_streams, "mix"), (out_w, n_streams, "out_w"), (in_w, n_streams, "in_w"),
+                          (gain, hidden, "gain"), (bias, hidden, "bias")):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != size):
+            raise KernelError(f"stream_mix_norm: {name} must be contiguous float32 with {size} entries")
+    n_rows = streams.shape[0] if rows is None else rows.numel()
+    dt = out.dtype if out is not None else pending.dtype if pending is not None else torch.float32
+    if out is not None and (out.shape != (n_rows, hidden) or not out.is_contiguous()):
+        raise KernelError("stream_mix_norm: out must be contiguous [rows, hidden]")
+    if pending is not None and (pending.shape != (streams.shape[0], hidden) or not pending.is_contiguous() or pending.dtype != dt):
+        raise KernelError("stream_mix_norm: the pending branch must be [N, hidden], contiguous, of the output's dtype")
+    lib.call("ns_stream_mix_norm", streams.data_ptr(), _ptr(pending), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(gain), _ptr(bias),
+             _ptr(out), _ptr(rows), n_rows, int(n_streams), hidden, float(eps), int(bool(centered)), dtype_code(dt), _stream())
+    return out
+
+
+def stream_read(streams: torch.Tensor, n_streams: int, pending: torch.Tensor | None, mix: torch.Tensor | None,
+                out_w: torch.Tensor | None, in_w: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    """out [N, H] float32 = sum_s in_w[s] x_s after the pending write, which is applied on the fly and not stored."""
+    _cuda(streams, pending, mix, out_w, in_w, out)
+    hidden = streams.shape[1] // n_streams
+    if out.dtype != torch.float32 or out.shape != (streams.shape[0], hidden) or not out.is_contiguous() or not streams.is_contiguous():
+        raise KernelError("stream_read: out must be contiguous float32 [N, hidden]")
+    lib.call("ns_stream_read", streams.data_ptr(), _ptr(pending), _ptr(mix), _ptr(out_w), _ptr(in_w), out.data_ptr(),
+             streams.shape[0], int(n_streams), hidden, dtype_code(pending.dtype if pending is not None else torch.float32), _stream())
+    return out
+
+
+def latent_rope_store(proj: torch.Tensor, ctx, lane, inv_freq: torch.Tensor | None, magnitude: float, gain: torch.Tensor,
+                      eps: float, heads: int, dim: int, rot_dim: int, rank: int, write: bool = True) -> None:
+    """Rows [q: heads * (dim + rot_dim) | raw latent: rank | key part: rot_dim | ...]: the rotated parts turn by position
+    (pairs (2i, 2i + 1), the first 2 * len(inv_freq) features of a part), q in place; the latent is RMS-normed with
+    `gain` and [latent | key part] goes to the token's slot of the lane's cache (csrc/latent.cu)."""
+    _cuda(proj, inv_freq, gain, lane.k)
+    if proj.stride(1) != 1 or proj.shape[1] < heads * (dim + rot_dim) + rank + rot_dim:
+        raise KernelError("latent_rope_store: rows of [q | latent | key part] with unit inner stride")
+    if gain.dtype != torch.float32 or gain.numel() != rank or (inv_freq is not None and (inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous())):
+        raise KernelError("latent_rope_store: float32 gain of the latent's size and float32 frequencies")
+    if write and (lane.k is None or lane.k.dtype != proj.dtype or not lane.k.is_contiguous() or lane.k.shape[-1] != rank + rot_dim
+                  or lane.k.shape[-3] != 1):
+        raise KernelError("latent_rope_store: the lane's cache must hold one vector of rank + rot_dim features per token")
+    bt = lane.block_table
+    lib.call("ns_latent_rope_store", proj.data_ptr(), proj.stride(0), ctx.positions.data_ptr(), ctx.token_req.data_ptr(),
+             _ptr(bt) if write else None, bt.stride(0) if write else 0, _ptr(inv_freq), float(magnitude),
+             inv_freq.numel() if inv_freq is not None else 0, gain.data_ptr(), float(eps), _ptr(lane.k) if write else None,
+             lane.page_size, heads, dim, rot_dim, rank, proj.shape[0], int(bool(write)), dtype_code(proj.dtype), _stream())
+
+
+USE_TENSOR_CORE_LATENT = True
+
+
+def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, lane, ctx, out: torch.Tensor, scale: float, window: int,
+                     sink: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of folded queries over a lane of cached latents.  q_lat [N, H, R] and q_rot [N, H, r] (any strides
+    with a unit inner one), out [N, H, R] likewise; `sink` [H] float32 joins each head's softmax denominator; `gate`
+    [N, H] (raw, a column range of a projection is fine): the head's output times its sigmoid."""
+    _cuda(q_lat, q_rot, out, sink, gate, lane.k)
+    n, H, R = q_lat.shape
+    r = q_rot.shape[2]
+    if q_rot.shape[:2] != (n, H) or out.shape != (n, H, R) or q_lat.stride(2) != 1 or (r and q_rot.stride(2) != 1) or out.stride(2) != 1:
+        raise KernelError("attention_latent: q_lat [N, H, R], q_rot [N, H, r], out [N, H, R] with unit inner strides")
+    if lane.k.dtype != q_lat.dtype or q_rot.dtype != q_lat.dtype or out.dtype != q_lat.dtype or lane.k.shape[-1] != R + r:
+        raise KernelError("attention_latent: operands and cache of one dtype, the cache R + r wide")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != H or not sink.is_contiguous()):
+        raise KernelError("attention_latent: one float32 sink per head")
+    if gate is not None and (gate.shape != (n, H) or gate.stride(1) != 1 or gate.dtype != q_lat.dtype):
+        raise KernelError("attention_latent: gate [N, H] with unit inner stride")
+    bt = lane.block_table
+    lib.call("ns_attention_latent", q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), q_rot.stride(0),
+             q_rot.stride(1), lane.k.data_ptr(), bt.data_ptr(), bt.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
+             _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0), out.stride(1),
+             n, H, R, r, lane.page_size, float(scale), int(window), dtype_code(q_lat.dtype), _stream())
+    return out
+
+
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x) elementwise in float, rounded once: "gelu_erf" (the exact gelu), "gelu_tanh", "silu"."""
+    _cuda(x, out)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind {kind!r} (known: {', '.join(ACTIVATIONS)})")
+    if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
+        raise KernelError("activation: contiguous operands of one shape and dtype")
+    lib.call("ns_activation", x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], dtype_code(x.dtype), _stream())
+    return out
+
+
+def cast_f32(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _cuda(x, out)
+    if out.dtype != torch.float32 or out.shape != x.shape or not out.is_contiguous() or x.stride(1) != 1:
+        raise KernelError("cast_f32: a contiguous float32 output of the input's shape")
+    lib.call("ns_cast_f32", x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], dtype_code(x.dtype), _stream())
+    return out
+
+
+def moe_route(logits: torch.Tensor, groups: int, keep: int, top: int, scale: float, ids: torch.Tensor, weights: torch.Tensor,
+              softmax: bool = False) -> None:
+    """Per row of float32 logits [N, E]: the chosen experts (int32 [N, top], largest score first) and their weights
+    (float32 [N, top]); see csrc/moe.cu for the rule."""
+    _cuda(logits, ids, weights)
+    n, E = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or ids.dtype != torch.int32 or weights.dtype != torch.float32 \
+            or ids.shape != (n, top) or weights.shape != (n, top) or not (ids.is_contiguous() and weights.is_contiguous()):
+        raise KernelError("moe_route: float32 logits [N, E], int32 ids and float32 weights [N, top], contiguous")
+    lib.call("ns_moe_route", logits.data_ptr(), n, E, int(groups), int(keep), int(top), float(scale), int(bool(softmax)),
+             ids.data_ptr(), weights.data_ptr(), _stream())
+
+
+def moe_plan(ids: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_of: torch.Tensor) -> None:
+    """offsets [E + 1] (running counts per expert) and row_of [N, top] (each pair's row where every expert's tokens lie
+    side by side), both int32."""
+    _cuda(ids, offsets, row_of)
+    for t, name in ((ids, "ids"), (offsets, "offsets"), (row_of, "row_of")):
+        _i32(t, name)
+    if offsets.numel() != n_experts + 1 or row_of.numel() != ids.numel():
+        raise KernelError("moe_plan: offsets [E + 1], row_of like ids")
+    lib.call("ns_moe_plan", ids.data_ptr(), ids.numel(), int(n_experts), offsets.data_ptr(), row_of.data_ptr(), _stream())
+
+
+def moe_gather(x: torch.Tensor, row_of: torch.Tensor, xs: torch.Tensor, top: int) -> torch.Tensor:
+    _cuda(x, row_of, xs)
+    n, width = x.shape
+    if xs.shape != (n * top, width) or xs.dtype != x.dtype or not (x.is_contiguous() and xs.is_contiguous()):
+        raise KernelError("moe_gather: xs [N * top, width] of x's dtype, contiguous")
+    lib.call("ns_moe_gather", x.data_ptr(), row_of.data_ptr(), xs.data_ptr(), n, int(top), width, dtype_code(x.dtype), _stream())
+    return xs
+
+
+def moe_combine(ys: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> torch.Tensor:
+    _cuda(ys, row_of, weights, out)
+    n, width = out.shape
+    if ys.shape != (n * top, width) or ys.dtype != out.dtype or not (ys.is_contiguous() and out.is_contiguous()):
+        raise KernelError("moe_combine: ys [N * top, width] of out's dtype, contiguous")
+    lib.call("ns_moe_combine", ys.data_ptr(), row_of.data_ptr(), weights.data_ptr(), out.data_ptr(), n, int(top), width,
+             dtype_code(out.dtype), _stream())
+    return out
+
+
+def moe_expert_rows(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                    w_down: torch.Tensor, act: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The chosen experts of a few tokens without a host round trip: w_gate, w_up [E, ff, width], w_down [E, width, ff]."""
+    _cuda(x, ids, weights, w_gate, w_up, w_down, act, out)
+    n, width = x.shape
+    top, ff = ids.shape[1], w_gate.shape[1]
+    if not all(t.is_contiguous() for t in (x, ids, weights, w_gate, w_up, w_down, act, out)) or act.shape != (n * top, ff) \
+            or out.shape != (n, width) or w_down.shape[1:] != (width, ff) or len({x.dtype, w_gate.dtype, w_up.dtype, w_down.dtype, act.dtype, out.dtype}) != 1:
+        raise KernelError("moe_expert_rows: contiguous operands of one dtype and the sizes the experts have")
+    lib.call("ns_moe_expert_rows", x.data_ptr(), ids.data_ptr(), weights.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(),
+             w_down.data_ptr(), act.data_ptr(), out.data_ptr(), n, top, width, ff, dtype_code(x.dtype), _stream())
+    return out

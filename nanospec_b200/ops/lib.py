@@ -53,6 +53,18 @@ _SIGNATURES: dict[str, list] = {
     "ns_attention_decode_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "ns_attention_prefill_kept": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "ns_attention_prefill": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "ns_stream_mix_norm": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
+    "ns_stream_read": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "ns_embed_streams": [_P, _P, _P, _I, _I, _I, _F, _I, _I, _P],
+    "ns_latent_rope_store": [_P, _I, _P, _P, _P, _I, _P, _F, _I, _P, _F, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ns_attention_latent": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _L, _L, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "ns_cast_f32": [_P, _L, _P, _I, _I, _I, _P],
+    "ns_moe_route": [_P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
+    "ns_moe_plan": [_P, _I, _I, _P, _P, _P],
+    "ns_moe_gather": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "ns_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "ns_moe_expert_rows": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "ns_activation": [_P, _P, _L, _I, _I, _P],
 }
 
 

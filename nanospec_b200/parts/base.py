@@ -60,7 +60,8 @@ class Part:
 class CacheNeed:
     """Paged key/value storage a mixer wants: per token `kv_heads * head_dim` keys and `kv_heads * v_dim`
     values (`v_dim` None: as wide as the keys); `window` > 0 means only the last `window` positions are ever
-    read, and beside them the first `keep_first` positions of the sequence."""
+    read, and beside them the first `keep_first` positions of the sequence.  `v_dim` 0: no values are stored (the
+    mixer reads keys and values out of one cached vector per token) and the lane's `v` is None."""
 
     kv_heads: int
     head_dim: int

@@ -14,12 +14,16 @@ from .registry import register_part
 
 @register_part("embedding", "table")
 class TokenEmbedding(Part):
-    """params: vocab, hidden, weight_name (the table's name after the part's prefix; default "weight")."""
+    """params: vocab, hidden, weight_name (the table's name after the part's prefix; default "weight"), scale (the rows
+    are multiplied by it; default 1) and copies (the stream is opened as so many equal copies side by side in a row,
+    for a block arrangement that keeps several; default 1)."""
 
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
         self.weight_name = spec.params.get("weight_name", "weight")
+        self.scale = float(spec.params.get("scale") or 1.0)
+        self.copies = int(spec.params.get("copies") or 1)
         self.table: torch.Tensor | None = None
 
     def weight_specs(self) -> dict[str, WeightSpec]:
@@ -29,6 +33,9 @@ class TokenEmbedding(Part):
         self.table = tensors[self.weight_name].contiguous()
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if self.scale != 1.0 or self.copies != 1:
+            return ops.embed_streams(self.table, ctx.token_ids, ctx.buffer("resid", self.copies * self.hidden, torch.float32),
+                                     self.scale, self.copies)
         return ops.embed(self.table, ctx.token_ids, ctx.buffer("resid", self.hidden, torch.float32))
 
 

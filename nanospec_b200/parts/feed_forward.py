@@ -63,3 +63,32 @@ class SwiGLU(Part):
         act = ops.gated_linear(x, self.w_gate_up, ctx.buffer("ffn_act", self.inter), ctx.buffer("gate_up", 2 * self.inter),
                                self.gate_block)
         return ops.linear(act, self.w_down, ctx.buffer("branch", self.hidden), sink=sink)
+
+
+@register_part("feed_forward", "dense_act")
+class DenseAct(Part):
+    """down(act(up(x))), no gate, no biases.  params: hidden, intermediate, activation ("gelu_erf": the exact gelu,
+    "gelu_tanh", "silu"), names (optional: keys "up", "down"; default "up", "down").  The activation is float32 on the
+    rounded product and is rounded once."""
+
+    def __init__(self, spec, dtype, device) -> None:
+        super().__init__(spec, dtype, device)
+        self.hidden, self.inter = int(spec["hidden"]), int(spec["intermediate"])
+        self.activation = spec.params.get("activation", "gelu_erf")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_act: unknown activation {self.activation!r} (known: {', '.join(ops.ACTIVATIONS)})")
+        names = dict(spec.params.get("names") or {})
+        self.n_up, self.n_down = names.get("up", "up"), names.get("down", "down")
+        self.w_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def weight_specs(self) -> dict[str, WeightSpec]:
+        return {self.n_up: WeightSpec((self.inter, self.hidden)), self.n_down: WeightSpec((self.hidden, self.inter))}
+
+    def bind(self, tensors) -> None:
+        self.w_up, self.w_down = tensors[self.n_up].contiguous(), tensors[self.n_down].contiguous()
+
+    def forward(self, x, ctx: StepContext):
+        u = ops.linear(x, self.w_up, ctx.buffer("ffn_up", self.inter))
+        a = ops.activation(u, ctx.buffer("ffn_act", self.inter), self.activation)
+        return ops.linear(a, self.w_down, ctx.buffer("branch", self.hidden))

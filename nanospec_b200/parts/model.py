@@ -96,6 +96,10 @@ class DecoderModel:
                 probe(i, resid, pending)
         if want_rows is None and not all_rows:
             return None
+        # an arrangement that keeps the stream in a form of its own (several copies) hands the final norm its input
+        close = getattr(self.blocks[order[-1].layer], "close", None) if order else None
+        if close is not None:
+            return close(resid, pending, self.final_norm, ctx, rows=want_rows, out_name="final_normed")
         return self.final_norm.add_norm(resid, pending, ctx, rows=want_rows, out_name="final_normed")
 
     def logits(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

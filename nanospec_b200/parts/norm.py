@@ -30,6 +30,9 @@ from .registry import register_part
 class RMSNorm(Part):
     """params: hidden, eps, weight_name (the gain's name after the norm's prefix; default "weight")."""
 
+    centered = False
+    bias: torch.Tensor | None = None
+
     def __init__(self, spec, dtype, device) -> None:
         super().__init__(spec, dtype, device)
         self.hidden = int(spec["hidden"])
@@ -60,11 +63,29 @@ class RMSNorm(Part):
 
 @register_part("norm", "layernorm")
 class LayerNorm(RMSNorm):
-    """(x - mean) / sqrt(var + eps) * gain: the variance is the mean of the squared deviations, there is no bias.
+    """(x - mean) / sqrt(var + eps) * gain (+ bias): the variance is the mean of the squared deviations.
     Mean and variance are taken in float32 in two passes over the row.  It has no `sink`: a centred norm is not a
-    per-row scale of the stream, so it is never folded into the products around it.  params as `rmsnorm`."""
+    per-row scale of the stream, so it is never folded into the products around it.  params as `rmsnorm`, and
+    bias_name (the bias's name after the norm's prefix; default None: no bias)."""
 
     sink = None  # hasattr(norm, "sink") is what the blocks ask; None says it cannot be folded
+    centered = True
+
+    def __init__(self, spec, dtype, device) -> None:
+        super().__init__(spec, dtype, device)
+        self.bias_name = spec.params.get("bias_name")
+        self.bias: torch.Tensor | None = None
+
+    def weight_specs(self) -> dict[str, WeightSpec]:
+        specs = super().weight_specs()
+        if self.bias_name is not None:
+            specs[self.bias_name] = WeightSpec((self.hidden,), rule="float32", init="normal")
+        return specs
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.bias_name is not None:
+            self.bias = tensors[self.bias_name].contiguous()
 
     def add_norm(self, resid: torch.Tensor, pending, ctx: StepContext,
                  rows: torch.Tensor | None = None, out_name: str = "normed"):
@@ -72,4 +93,6 @@ class LayerNorm(RMSNorm):
             raise ValueError("a RowScaled reached a norm that cannot take it")
         n = resid.shape[0] if rows is None else rows.numel()
         out = ctx.buffer(out_name, self.hidden, rows=n)
+        if self.bias is not None:  # the kernel of the streams, on one stream: the residual sum, the norm and its bias
+            return ops.stream_mix_norm(resid, 1, pending, None, None, None, self.gain, self.bias, self.eps, True, out, rows=rows)
         return ops.add_layernorm(resid, pending, self.gain, self.eps, out, rows=rows)
