@@ -58,7 +58,12 @@ def yarn_frequencies(rot: dict):
 
 
 def rotate_interleaved(x, positions, rot: dict):
-    """x [T, ..., dims]: the pair (2i, 2i+1) turns by positions * f_i."""
+    """x [T, ..., n]: the pair (2i, 2i+1) of the first rot.dims features turns by positions * f_i; the rest pass."""
+    if not rot or x.shape[-1] == 0:
+        return x
+    dims = int(rot["dims"])
+    if dims < x.shape[-1]:
+        return torch.cat([rotate_interleaved(x[..., :dims], positions, rot), x[..., dims:]], dim=-1)
     f, mag = yarn_frequencies(rot)
     ang = positions.to(F)[:, None] * f[None, :]                  # [T, dims/2]
     while ang.dim() < x.dim():
@@ -77,13 +82,13 @@ def latent_attention(h, w: dict, m: dict, eps: float, kind: str):
     H, d, r, dv, R = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
     pos = torch.arange(T)
     q = (h @ w["q"].T).view(T, H, d + r)
-    q_plain, q_rot = q[..., :d], rotate_interleaved(q[..., d:], pos, m["rot"])
+    q_plain, q_rot = q[..., :d], rotate_interleaved(q[..., d:], pos, m.get("rot"))
     dkv = h @ w["dkv"].T
     c = rms_norm(dkv[:, :R], w["dkv.norm"], eps)
-    k_rot = rotate_interleaved(dkv[:, R:], pos, m["rot"])           # [T, r], shared by the heads
+    k_rot = rotate_interleaved(dkv[:, R:], pos, m.get("rot"))           # [T, r], shared by the heads
     k_plain = (c @ w["uk"].T).view(T, H, d)
     v = (c @ w["uv"].T).view(T, H, dv)
-    window = int(m["mask"]["size"])
+    window = int(m["mask"]["size"]) if m.get("mask") else T + 1
     out = torch.zeros(T, H, dv, dtype=F)
     for hh in range(H):
         s = (q_plain[:, hh] @ k_plain[:, hh].T + q_rot[:, hh] @ k_rot.T) * float(m["scale"])   # [query, key]
