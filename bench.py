@@ -25,7 +25,9 @@ file when present.
 (windowed attention with kept first keys, retention, gated delta rule; random weights) at two sizes that resemble real
 layers, each beside a Llama model of equal width, feed-forward, heads and layer count, and every kernel of one prefill
 step and one decode step of both, timed alone and set against its own bound (bytes over the copy peak, tensor flops over
-the tensor peak, CUDA-core flops over the nominal float32 rate).
+the tensor peak, CUDA-core flops over the nominal float32 rate).  `--design sorizen` does the same for Sorizen models (attention
+over a cached latent with a sink or a gate, hyper-connections, dense and routed feed-forwards) beside Dezolorn models of
+windowed attention layers alone.
 """
 
 from __future__ import annotations
@@ -604,6 +606,135 @@ def run_design(args) -> dict:
     }
 
 
+# ---- Sorizen beside a Dezolorn model of attention layers alone (--design sorizen) -------------------------------------------
+
+SORIZEN_SIZES = {
+    # width, dense feed-forward, heads, plain / rotated / value head sizes, latent, experts (count, chosen, width, groups, kept), layers
+    "w2048": dict(width=2048, ff=8192, heads=16, kv_heads=8, dim=128, rot_dim=64, vdim=128, rank=512, experts=32, top=4, eff=1024,
+                  groups=4, keep=2, streams=2, layers=8),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, rot_dim=64, vdim=128, rank=512, experts=32, top=4, eff=2048,
+                  groups=4, keep=2, streams=2, layers=4),
+}
+SORIZEN_WINDOW = 1024
+
+
+def sorizen_config(sz: dict) -> dict:
+    def mixer():
+        return {"heads": sz["heads"], "dim": sz["dim"], "rot_dim": sz["rot_dim"], "vdim": sz["vdim"], "kv_rank": sz["rank"],
+                "scale": (sz["dim"] + sz["rot_dim"]) ** -0.5, "mask": {"size": SORIZEN_WINDOW},
+                "rot": {"dims": sz["rot_dim"], "base": 1000000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}
+    dense = {"type": "latent_attention_2", "mixer": mixer(), "mlp": {"kind": "dense", "ff": sz["ff"]}}
+    routed = {"type": "latent_attention", "mixer": mixer(), "mlp": {"kind": "moe", "expert": {"ff": sz["eff"]}, "router": {
+        "experts": sz["experts"], "top": sz["top"], "scale": 2.0, "groups": {"count": sz["groups"], "keep": sz["keep"]}}}}
+    return {"architecture": "Sorizen", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "streams": sz["streams"], "layers": [dense if i % 2 == 0 else routed for i in range(sz["layers"])]}
+
+
+def windowed_sibling(sz: dict) -> dict:
+    """The closest model the framework had: Dezolorn layers of windowed attention alone (layer norm, rotation with scaling, a
+    gated feed-forward), at the same width, feed-forward, heads and layer count."""
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": sz["ff"]}, "mixer": {
+        "heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+        "mask": {"size": SORIZEN_WINDOW, "keep_first": 0},
+        "rot": {"dims": sz["dim"], "base": 1000000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}}
+    return {"architecture": "Dezolorn", "vocab": DESIGN_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6},
+            "layers": [attention] * sz["layers"], "loop": {"start": 0, "stop": 0, "times": 1}, "logit_scale": 1.0, "logit_softcap": 0.0}
+
+
+def sorizen_bounds(kind: str, sz: dict, tokens: int, batch: int, context: int, pk: dict) -> dict[str, float]:
+    """Seconds that every kernel of one step needs at least, over all its calls (see kernel_bounds)."""
+    N = tokens or batch
+    W, L, H = sz["width"], sz["layers"], sz["heads"]
+    bw, tc = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    seen = lambda p: min(p + 1, SORIZEN_WINDOW)
+    pairs = sum(seen(p) for p in range(tokens)) if tokens else batch * seen(context)
+    out: dict[str, float] = {}
+    if kind == "dezolorn":
+        nkv, d = sz["kv_heads"], sz["dim"]
+        out["ns_add_layernorm"] = 2 * L * 12.0 * N * W / bw
+        out["ns_qk_norm_rope_store"] = L * 2.0 * N * ((H + nkv) * d * 2 + nkv * d + 2 * nkv * d) / bw
+        if tokens:
+            out["ns_attention_prefill_kept"] = L * 4.0 * H * d * pairs / tc
+        else:
+            out["ns_attention_decode_kept"] = L * 4.0 * pairs * nkv * d / bw
+        out["ns_swiglu"] = L * 6.0 * N * sz["ff"] / bw
+        return out
+    S, R, r, d = sz["streams"], sz["rank"], sz["rot_dim"], sz["dim"]
+    n_dense, n_moe = (L + 1) // 2, L // 2
+    # the copies read and written in float32, the branch read and the normed row written in bfloat16 (the last call of a step
+    # reads only); one call per sublayer and one at the end
+    out["ns_stream_mix_norm"] = (2 * L + 1) * N * (8.0 * S * W + 4.0 * W) / bw
+    out["ns_embed_streams"] = N * (2.0 * W + 4.0 * S * W) / bw
+    out["ns_latent_rope_store"] = L * N * 2.0 * (2 * H * r + 2 * (R + r)) / bw
+    if tokens:  # scores over R + r features and sums over R per (query, key, head), on the tensor cores
+        out["ns_attention_latent"] = L * 2.0 * H * (2 * R + r) * pairs / tc
+    else:       # every visible latent once per request: the heads share it
+        out["ns_attention_latent"] = L * 2.0 * pairs * (R + r) / bw
+    out["ns_activation"] = n_dense * 4.0 * N * sz["ff"] / bw
+    E, top, eff = sz["experts"], sz["top"], sz["eff"]
+    out["ns_cast_f32"] = n_moe * 6.0 * N * W / bw
+    if tokens:
+        out["ns_moe_gather"] = n_moe * 4.0 * N * top * W / bw
+        out["ns_moe_combine"] = n_moe * 2.0 * N * (top + 1) * W / bw
+        out["ns_swiglu"] = n_moe * 6.0 * N * top * eff / bw
+    else:       # the weights of the experts that the step's tokens chose, once
+        out["ns_moe_expert_rows"] = n_moe * min(E, batch * top) * 6.0 * eff * W / bw
+    return out
+
+
+def run_design_sorizen(args) -> dict:
+    import torch
+
+    from nanospec_b200 import random_model
+
+    pk, pk_src = peaks()
+    out_sizes = {}
+    for name, sz in SORIZEN_SIZES.items():
+        row = {}
+        for kind in ("sorizen", "dezolorn"):
+            cfg = sorizen_config(sz) if kind == "sorizen" else windowed_sibling(sz)
+            model = random_model(cfg, seed=1, device="cuda", dtype=torch.bfloat16)
+            pages_per_req = -(-(CONTEXT + args.repeats * args.steps + args.warmup + 64) // PAGE)
+            eng = design_engine(model, 64, max(64 * pages_per_req, -(-PREFILL_TOKENS // PAGE) + 8) + 8)
+            rec = {}
+            for b in (8, 64):
+                pt = time_decode(eng, b, args.steps, args.warmup, args.repeats)
+                rec[f"decode_b{b}_tok_s"] = round(b * 1000.0 / pt["ms"], 1)
+                rec[f"decode_b{b}_ms"] = round(pt["ms"], 4)
+                rec[f"decode_b{b}_clocks"] = {"sm_mhz": pt["clocks"].get("sm_mhz"), "reasons": pt["clocks"].get("reasons")}
+                if b == 8 and kind == "sorizen" and name == "w4096":
+                    headline = pt
+            pre_ms, pre_clocks = time_prefill(eng, warmup=3, iters=5)
+            rec["prefill_tok_s"] = round(PREFILL_TOKENS * 1000.0 / pre_ms, 1)
+            rec["prefill_ms"] = round(pre_ms, 3)
+            rec["prefill_clocks"] = {"sm_mhz": pre_clocks.get("sm_mhz"), "reasons": pre_clocks.get("reasons")}
+            del eng
+            torch.cuda.empty_cache()
+            kernels = {}
+            for what, tokens, batch in (("prefill", PREFILL_TOKENS, 0), ("decode_b64", 0, 64)):
+                timed = time_kernels(model, tokens, batch, CONTEXT)
+                bounds = sorizen_bounds(kind, sz, tokens, batch, CONTEXT, pk)
+                kernels[what] = {k: {"calls": n, "ms": round(ms, 4), "bound_ms": round(bounds[k] * 1e3, 4) if k in bounds else None,
+                                     "frac": round(bounds[k] * 1e3 / ms, 4) if k in bounds and ms > 0 else None}
+                                 for k, (n, ms) in sorted(timed.items(), key=lambda kv: -kv[1][1])}
+            rec["kernels"] = kernels
+            row[kind] = rec
+            del model
+            torch.cuda.empty_cache()
+        out_sizes[name] = row
+    value = out_sizes["w4096"]["sorizen"]["decode_b8_tok_s"]
+    return {
+        "metric": "decode tok/s (Sorizen, width 4,096, 4 layers, batch 8, 1,024-token context)", "value": value, "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": out_sizes["w4096"]["sorizen"]["decode_b8_ms"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform random token ids, random weights",
+        "config": {"design": "sorizen beside dezolorn (attention layers)", "sizes": SORIZEN_SIZES, "vocab": DESIGN_VOCAB,
+                   "window": SORIZEN_WINDOW, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "page": PAGE, "cuda_graphs": True,
+                   "peaks": pk_src, "l2": "the weights of every step are larger than L2"},
+        "gpu_launches": headline["launches"], "clocks": headline["clocks"], "sizes": out_sizes,
+    }
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
 
@@ -620,7 +751,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"])
     ap.add_argument("--no-workloads", action="store_true", help="leave out the 3B continuous-batching and 1B mixed workloads")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--design", choices=["dezolorn"], help="measure this design beside the Llama model of equal size instead")
+    ap.add_argument("--design", choices=["dezolorn", "sorizen"], help="measure this design beside its closest sibling of equal size instead")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     args.repeats = max(1, args.repeats)
@@ -628,7 +759,7 @@ def main() -> int:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2
-    out = run_reference(args) if args.impl == "reference" else run_design(args) if args.design else run_ours(args)
+    out = run_reference(args) if args.impl == "reference" else run_design_sorizen(args) if args.design == "sorizen" else run_design(args) if args.design else run_ours(args)
     print(json.dumps(out), flush=True)
     return 0
 

@@ -918,7 +918,10 @@ def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, lane, ctx, out: t
                      sink: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of folded queries over a lane of cached latents.  q_lat [N, H, R] and q_rot [N, H, r] (any strides
     with a unit inner one), out [N, H, R] likewise; `sink` [H] float32 joins each head's softmax denominator; `gate`
-    [N, H] (raw, a column range of a projection is fine): the head's output times its sigmoid."""
+    [N, H] (raw, a column range of a projection is fine): the head's output times its sigmoid.
+    bfloat16 with a latent and a rotated part in multiples of 16 (the latent up to 512): the tensor-core kernel
+    (csrc/latent_tc.cu), the keys of a token split over blocks when the step has few tokens; float32 and other sizes:
+    the exact kernel (csrc/latent.cu)."""
     _cuda(q_lat, q_rot, out, sink, gate, lane.k)
     n, H, R = q_lat.shape
     r = q_rot.shape[2]
@@ -931,6 +934,24 @@ def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, lane, ctx, out: t
     if gate is not None and (gate.shape != (n, H) or gate.stride(1) != 1 or gate.dtype != q_lat.dtype):
         raise KernelError("attention_latent: gate [N, H] with unit inner stride")
     bt = lane.block_table
+    if USE_TENSOR_CORE_LATENT and q_lat.dtype == torch.bfloat16 and R % 16 == 0 and r % 16 == 0 and R <= 512 \
+            and out.stride(0) % 2 == 0 and out.stride(1) % 2 == 0 and out.data_ptr() % 4 == 0:
+        groups = -(-H // 16)
+        blocks = n * groups
+        # few (token, head group) pairs: the keys of a token are split over blocks, whole tiles of 64 each
+        longest = ctx.max_kv_len or 1
+        tiles = -(-(min(window, longest) if window else longest) // 64)
+        n_splits = max(1, min(16, tiles, (2 * sm_count()) // blocks))
+        part_o = part_ml = None
+        if n_splits > 1:
+            ws = ctx.workspace
+            part_o = ws.get("latent_part_o", blocks * n_splits * 16, R, torch.float32)
+            part_ml = ws.get("latent_part_ml", blocks * n_splits * 16, 2, torch.float32)
+        lib.call("ns_attention_latent_tc", q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), q_rot.stride(0),
+                 q_rot.stride(1), lane.k.data_ptr(), bt.data_ptr(), bt.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
+                 _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0), out.stride(1),
+                 _ptr(part_o), _ptr(part_ml), n, H, R, r, lane.page_size, float(scale), int(window), n_splits, _stream())
+        return out
     lib.call("ns_attention_latent", q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), q_rot.stride(0),
              q_rot.stride(1), lane.k.data_ptr(), bt.data_ptr(), bt.stride(0), ctx.token_req.data_ptr(), ctx.positions.data_ptr(),
              _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0), out.stride(1),
