@@ -667,12 +667,12 @@ def sorizen_bounds(kind: str, sz: dict, tokens: int, batch: int, context: int, p
     out["ns_embed_streams"] = N * (2.0 * W + 4.0 * S * W) / bw
     out["ns_latent_rope_store"] = L * N * 2.0 * (2 * H * r + 2 * (R + r)) / bw
     if tokens:  # scores over R + r features and sums over R per (query, key, head), on the tensor cores
-        out["ns_attention_latent"] = L * 2.0 * H * (2 * R + r) * pairs / tc
+        out["ns_attention_latent_tc"] = L * 2.0 * H * (2 * R + r) * pairs / tc
     else:       # every visible latent once per request: the heads share it
-        out["ns_attention_latent"] = L * 2.0 * pairs * (R + r) / bw
+        out["ns_attention_latent_tc"] = L * 2.0 * pairs * (R + r) / bw
     out["ns_activation"] = n_dense * 4.0 * N * sz["ff"] / bw
     E, top, eff = sz["experts"], sz["top"], sz["eff"]
-    out["ns_cast_f32"] = n_moe * 6.0 * N * W / bw
+    out["ns_router_logits"] = n_moe * (2.0 * N * W + 4.0 * E * W) / bw
     if tokens:
         out["ns_moe_gather"] = n_moe * 4.0 * N * top * W / bw
         out["ns_moe_combine"] = n_moe * 2.0 * N * (top + 1) * W / bw

@@ -18,7 +18,18 @@ namespace {
 
 constexpr int kMaxStreams = 8;
 
-template <typename T>
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, const float* __restrict__ mix,
                        const float* __restrict__ outw, const float* __restrict__ inw, const float* __restrict__ gain,
@@ -40,36 +51,60 @@ stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, con
     float* xs = streams + (size_t)row * S * hidden;
     const T* yr = y ? y + (size_t)row * hidden : nullptr;
     float sum = 0.f;
-    for (int h = tid; h < hidden; h += blockDim.x) {
-        float x[kMaxStreams];
+    // four neighbouring features per thread and turn when rows start on 16 bytes (VEC), one otherwise
+    for (int h = tid * VEC; h < hidden; h += blockDim.x * VEC) {
+        float x[kMaxStreams][VEC];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) x[s] = s < S ? xs[(size_t)s * hidden + h] : 0.f;
-        if (yr) {
-            const float yv = ns_ld(yr, h);
-            float nx[kMaxStreams];
-#pragma unroll
-            for (int t = 0; t < kMaxStreams; ++t) {
-                float a = 0.f;
-                if (t < S) {
-#pragma unroll
-                    for (int s = 0; s < kMaxStreams; ++s)
-                        if (s < S) a = fmaf(c_mix[s * S + t], x[s], a);
-                    a = fmaf(c_out[t], yv, a);
+        for (int s = 0; s < kMaxStreams; ++s) {
+            if (s < S) {
+                if constexpr (VEC == 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)s * hidden + h);
+                    x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
+                } else {
+                    x[s][0] = xs[(size_t)s * hidden + h];
                 }
-                nx[t] = a;
-            }
+            } else {
 #pragma unroll
-            for (int t = 0; t < kMaxStreams; ++t) {
-                x[t] = nx[t];
-                if (write_back && t < S) xs[(size_t)t * hidden + h] = nx[t];
+                for (int i = 0; i < VEC; ++i) x[s][i] = 0.f;
             }
         }
-        float u = 0.f;
+        if (yr) {
+            float yv[VEC];
+            if constexpr (VEC == 4) ld4(yr + h, yv); else yv[0] = ns_ld(yr, h);
+            float nx[kMaxStreams][VEC];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s)
-            if (s < S) u = fmaf(c_in[s], x[s], u);
-        u_row[h] = u;
-        sum += centered ? u : u * u;
+            for (int t = 0; t < kMaxStreams; ++t) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    float a = 0.f;
+                    if (t < S) {
+#pragma unroll
+                        for (int s = 0; s < kMaxStreams; ++s)
+                            if (s < S) a = fmaf(c_mix[s * S + t], x[s][i], a);
+                        a = fmaf(c_out[t], yv[i], a);
+                    }
+                    nx[t][i] = a;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < kMaxStreams; ++t) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) x[t][i] = nx[t][i];
+                if (write_back && t < S) {
+                    if constexpr (VEC == 4) *reinterpret_cast<float4*>(xs + (size_t)t * hidden + h) = make_float4(nx[t][0], nx[t][1], nx[t][2], nx[t][3]);
+                    else xs[(size_t)t * hidden + h] = nx[t][0];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < kMaxStreams; ++s)
+                if (s < S) u = fmaf(c_in[s], x[s][i], u);
+            u_row[h + i] = u;
+            sum += centered ? u : u * u;
+        }
     }
     if (!out) return;  // only the streams were wanted
     T* o = out + (size_t)j * hidden;
@@ -152,17 +187,23 @@ NS_API int ns_stream_mix_norm(float* streams, const void* y, const float* mix, c
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_stream_mix_norm: a row of %d floats does not fit shared memory", hidden);
     const int write_back = rows ? 0 : 1;
+    // which kernel runs depends on the width and the alignment only, never on the batch
+    const bool vec = hidden % 4 == 0 && (((uintptr_t)streams | (uintptr_t)y) % 16 == 0);
+    const int threads = hidden >= 1024 ? 256 : 128;
+#define NS_STREAM_LAUNCH(T, V)                                                                                                   \
+    {                                                                                                                            \
+        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+        NS_LAUNCH((stream_mix_norm_kernel<T, V>), n_rows, threads, smem, stream, streams, (const T*)y, mix, outw, inw, gain, bias, (T*)out, \
+                  rows, S, hidden, eps, centered, write_back);                                                                   \
+    }
     if (dtype == NS_F32) {
-        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        NS_LAUNCH((stream_mix_norm_kernel<float>), n_rows, 256, smem, stream, streams, (const float*)y, mix, outw, inw, gain, bias,
-                  (float*)out, rows, S, hidden, eps, centered, write_back);
+        if (vec) NS_STREAM_LAUNCH(float, 4) else NS_STREAM_LAUNCH(float, 1)
     } else if (dtype == NS_BF16) {
-        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        NS_LAUNCH((stream_mix_norm_kernel<__nv_bfloat16>), n_rows, 256, smem, stream, streams, (const __nv_bfloat16*)y, mix, outw,
-                  inw, gain, bias, (__nv_bfloat16*)out, rows, S, hidden, eps, centered, write_back);
+        if (vec) NS_STREAM_LAUNCH(__nv_bfloat16, 4) else NS_STREAM_LAUNCH(__nv_bfloat16, 1)
     } else {
         NS_FAIL(NS_ERR_ARGUMENT, "ns_stream_mix_norm: unknown dtype %d", dtype);
     }
+#undef NS_STREAM_LAUNCH
     NS_CHECK_LAUNCH("ns_stream_mix_norm");
     return NS_OK;
 }

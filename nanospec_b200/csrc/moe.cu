@@ -2,6 +2,7 @@
 // the experts' products for steps of a few tokens.
 //
 //   ns_cast_f32        rows of the compute type as float (the router's input: its logits are a float product)
+//   ns_router_logits   the router's float product for a few tokens (longer steps: ns_cast_f32 and the float GEMM)
 //   ns_moe_route       scores = sigmoid(logits) (or softmax); experts in `groups` equal runs of neighbours, a group's
 //                      score the sum of its two largest scores, only the best `keep` groups eligible; the `top`
 //                      eligible experts with the largest scores; weights = score / (sum of the chosen + 1e-20) * scale.
@@ -27,6 +28,35 @@ __global__ void cast_f32_kernel(const T* __restrict__ x, long long ldx, float* _
 }
 
 constexpr int kMaxExperts = 1024;
+
+// logits[n, e] = x[n] . w[e] in float, for steps of a few tokens: a block per token, its row in shared memory,
+// a warp per expert in turn (the sum over the row in a fixed order)
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w, float* __restrict__ logits, int E, int K) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    extern __shared__ float xrow[];
+    const int n = blockIdx.x, lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xrow[k] = ns_ld(x, (size_t)n * ldx + k);
+    __syncthreads();
+    const bool vec = K % 4 == 0 && ((uintptr_t)w % 16 == 0);
+    for (int e = wib; e < E; e += 8) {
+        const float* wr = w + (size_t)e * K;
+        float a = 0.f;
+        if (vec) {
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(wr + k);
+                const float4 u = *reinterpret_cast<const float4*>(xrow + k);
+                a = fmaf(v.x, u.x, a); a = fmaf(v.y, u.y, a); a = fmaf(v.z, u.z, a); a = fmaf(v.w, u.w, a);
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) a = fmaf(wr[k], xrow[k], a);
+        }
+        a = ns_warp_sum(a);
+        if (lane == 0) logits[(size_t)n * E + e] = a;
+    }
+}
 
 // one warp per token
 __global__ void __launch_bounds__(128)
@@ -117,12 +147,14 @@ moe_route_kernel(const float* __restrict__ logits, int n_tokens, int E, int grou
         ids[(size_t)n * top + lane] = mine_id;
         weights[(size_t)n * top + lane] = mine * f;
     }
+    __syncwarp();
     for (int k = 32 + lane; k < top; k += 32) weights[(size_t)n * top + k] *= f;
 }
 
 // one block: counts, offsets, rows
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ offsets, int* __restrict__ row_of) {
+moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ offsets, int* __restrict__ row_of,
+                int* __restrict__ pair_of) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
     __shared__ int count[kMaxExperts], cursor[kMaxExperts];
@@ -142,7 +174,11 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict
     }
     __syncthreads();
     // which row of its expert's run a pair gets does not matter to any result: rows are computed alone
-    for (int i = tid; i < n_pairs; i += blockDim.x) row_of[i] = atomicAdd(&cursor[ids[i]], 1);
+    for (int i = tid; i < n_pairs; i += blockDim.x) {
+        const int row = atomicAdd(&cursor[ids[i]], 1);
+        row_of[i] = row;
+        if (pair_of) pair_of[row] = i;
+    }
 }
 
 template <typename T>
@@ -232,18 +268,32 @@ moe_down_rows_kernel(const T* __restrict__ act, const int* __restrict__ ids, con
     }
 }
 
+__device__ __forceinline__ float act_value(float z, int kind) {
+    if (kind == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    return z / (1.f + expf(-z));
+}
+
+template <typename T>
+__global__ void activation_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int kind, size_t total8) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    float v[8];
+    ld8(x + i * 8, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = act_value(v[k], kind);
+    st8(out + i * 8, v);
+}
+
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, int kind, size_t total) {
     ns_pdl_launch_dependents();
     ns_pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const float z = ns_ld(x, i);
-    float v;
-    if (kind == 0) v = 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
-    else if (kind == 1) v = 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-    else v = z / (1.f + expf(-z));
-    ns_st(out, i, v);
+    ns_st(out, i, act_value(ns_ld(x, i), kind));
 }
 
 }  // namespace
@@ -259,6 +309,25 @@ NS_API int ns_cast_f32(const void* x, long long ldx, float* out, int n_rows, int
     return NS_OK;
 }
 
+// x [n, K] (row stride ldx) in the compute type, w [E, K] float, logits [n, E] float
+NS_API int ns_router_logits(const void* x, long long ldx, const float* w, float* logits, int n_tokens, int E, int K, int dtype,
+                            cudaStream_t stream) {
+    if (n_tokens <= 0) return NS_OK;
+    const size_t smem = (size_t)K * sizeof(float);
+    if (smem > 200 * 1024) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_router_logits: a row of %d floats does not fit shared memory", K);
+    if (dtype == NS_F32) {
+        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(router_logits_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        NS_LAUNCH((router_logits_kernel<float>), n_tokens, 256, smem, stream, (const float*)x, ldx, w, logits, E, K);
+    } else if (dtype == NS_BF16) {
+        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(router_logits_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        NS_LAUNCH((router_logits_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)x, ldx, w, logits, E, K);
+    } else {
+        NS_FAIL(NS_ERR_ARGUMENT, "ns_router_logits: unknown dtype %d", dtype);
+    }
+    NS_CHECK_LAUNCH("ns_router_logits");
+    return NS_OK;
+}
+
 NS_API int ns_moe_route(const float* logits, int n_tokens, int E, int groups, int keep, int top, float scale, int softmax,
                         int* ids, float* weights, cudaStream_t stream) {
     if (n_tokens <= 0) return NS_OK;
@@ -271,9 +340,10 @@ NS_API int ns_moe_route(const float* logits, int n_tokens, int E, int groups, in
     return NS_OK;
 }
 
-NS_API int ns_moe_plan(const int* ids, int n_pairs, int E, int* offsets, int* row_of, cudaStream_t stream) {
+// pair_of (optional): the inverse of row_of
+NS_API int ns_moe_plan(const int* ids, int n_pairs, int E, int* offsets, int* row_of, int* pair_of, cudaStream_t stream) {
     if (E < 1 || E > kMaxExperts) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_moe_plan: %d experts (at most %d)", E, kMaxExperts);
-    NS_LAUNCH(moe_plan_kernel, 1, 1024, 0, stream, ids, n_pairs, E, offsets, row_of);
+    NS_LAUNCH(moe_plan_kernel, 1, 1024, 0, stream, ids, n_pairs, E, offsets, row_of, pair_of);
     NS_CHECK_LAUNCH("ns_moe_plan");
     return NS_OK;
 }
@@ -330,6 +400,15 @@ NS_API int ns_moe_expert_rows(const void* x, const int* ids, const float* weight
 NS_API int ns_activation(const void* x, void* out, long long total, int kind, int dtype, cudaStream_t stream) {
     if (total <= 0) return NS_OK;
     if (kind < 0 || kind > 2) NS_FAIL(NS_ERR_ARGUMENT, "ns_activation: unknown kind %d", kind);
+    if (total % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) % 16 == 0)) {  // eight elements to a thread
+        const size_t total8 = (size_t)total / 8;
+        const unsigned vblocks = (unsigned)((total8 + 255) / 256);
+        if (dtype == NS_F32) NS_LAUNCH((activation_vec_kernel<float>), vblocks, 256, 0, stream, (const float*)x, (float*)out, kind, total8);
+        else if (dtype == NS_BF16) NS_LAUNCH((activation_vec_kernel<__nv_bfloat16>), vblocks, 256, 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, kind, total8);
+        else NS_FAIL(NS_ERR_ARGUMENT, "ns_activation: unknown dtype %d", dtype);
+        NS_CHECK_LAUNCH("ns_activation");
+        return NS_OK;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == NS_F32) NS_LAUNCH((activation_kernel<float>), blocks, 256, 0, stream, (const float*)x, (float*)out, kind, (size_t)total);
     else if (dtype == NS_BF16) NS_LAUNCH((activation_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, kind, (size_t)total);

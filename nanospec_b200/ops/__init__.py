@@ -912,6 +912,7 @@ def latent_rope_store(proj: torch.Tensor, ctx, lane, inv_freq: torch.Tensor | No
 
 
 USE_TENSOR_CORE_LATENT = True
+LATENT_BLOCKS_PER_SM = 2  # the tensor-core latent kernel splits a token's keys until the grid holds about this many blocks per SM
 
 
 def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, lane, ctx, out: torch.Tensor, scale: float, window: int,
@@ -941,7 +942,7 @@ def attention_latent(q_lat: torch.Tensor, q_rot: torch.Tensor, lane, ctx, out: t
         # few (token, head group) pairs: the keys of a token are split over blocks, whole tiles of 64 each
         longest = ctx.max_kv_len or 1
         tiles = -(-(min(window, longest) if window else longest) // 64)
-        n_splits = max(1, min(16, tiles, (2 * sm_count()) // blocks))
+        n_splits = max(1, min(16, tiles, (LATENT_BLOCKS_PER_SM * sm_count()) // blocks))
         part_o = part_ml = None
         if n_splits > 1:
             ws = ctx.workspace
@@ -981,6 +982,27 @@ def cast_f32(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+# the router's logits come from ns_router_logits (every token's block reads the whole router, from L2) while tokens x
+# experts x width stays under this; beyond it from the float32 GEMM, which reads the router once per 64 tokens
+ROUTER_DIRECT_MAX = 1 << 28
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch=None) -> torch.Tensor:
+    """out [N, E] float32 = x @ w^T with float32 products and sums, x in the compute type, w [E, K] float32.  A few tokens:
+    one kernel, a warp per (token, expert); many tokens and a large router: x as float32 (into `scratch(...)`'s buffer) and the float32 GEMM."""
+    _cuda(x, w, out)
+    n, K = x.shape
+    E = w.shape[0]
+    if w.dtype != torch.float32 or out.dtype != torch.float32 or out.shape != (n, E) or not (w.is_contiguous() and out.is_contiguous()) \
+            or x.stride(1) != 1 or w.shape[1] != K:
+        raise KernelError("router_logits: float32 router [E, K] and logits [N, E], contiguous; x rows with unit inner stride")
+    if n * E * K <= ROUTER_DIRECT_MAX or n <= 64:
+        lib.call("ns_router_logits", x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), n, E, K, dtype_code(x.dtype), _stream())
+        return out
+    x32 = x if x.dtype == torch.float32 else cast_f32(x, scratch(n, K))
+    return linear(x32, w, out)
+
+
 def moe_route(logits: torch.Tensor, groups: int, keep: int, top: int, scale: float, ids: torch.Tensor, weights: torch.Tensor,
               softmax: bool = False) -> None:
     """Per row of float32 logits [N, E]: the chosen experts (int32 [N, top], largest score first) and their weights
@@ -994,15 +1016,35 @@ def moe_route(logits: torch.Tensor, groups: int, keep: int, top: int, scale: flo
              ids.data_ptr(), weights.data_ptr(), _stream())
 
 
-def moe_plan(ids: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_of: torch.Tensor) -> None:
-    """offsets [E + 1] (running counts per expert) and row_of [N, top] (each pair's row where every expert's tokens lie
-    side by side), both int32."""
-    _cuda(ids, offsets, row_of)
-    for t, name in ((ids, "ids"), (offsets, "offsets"), (row_of, "row_of")):
+def moe_plan(ids: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_of: torch.Tensor, pair_of: torch.Tensor | None = None) -> None:
+    """offsets [E + 1] (running counts per expert), row_of [N, top] (each pair's row where every expert's tokens lie
+    side by side) and, when given, pair_of (the pair at each row), all int32."""
+    _cuda(ids, offsets, row_of, pair_of)
+    for t, name in ((ids, "ids"), (offsets, "offsets"), (row_of, "row_of"), (pair_of, "pair_of")):
         _i32(t, name)
-    if offsets.numel() != n_experts + 1 or row_of.numel() != ids.numel():
-        raise KernelError("moe_plan: offsets [E + 1], row_of like ids")
-    lib.call("ns_moe_plan", ids.data_ptr(), ids.numel(), int(n_experts), offsets.data_ptr(), row_of.data_ptr(), _stream())
+    if offsets.numel() != n_experts + 1 or row_of.numel() != ids.numel() or (pair_of is not None and pair_of.numel() != ids.numel()):
+        raise KernelError("moe_plan: offsets [E + 1], row_of and pair_of like ids")
+    lib.call("ns_moe_plan", ids.data_ptr(), ids.numel(), int(n_experts), offsets.data_ptr(), row_of.data_ptr(), _ptr(pair_of), _stream())
+
+
+def moe_grouped_ok(x: torch.Tensor, width: int, ff: int) -> bool:
+    """Whether the tensor-core kernel of the grouped experts takes these operands (bfloat16, widths in multiples of 8)."""
+    return x.dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0 and x.is_contiguous() and x.data_ptr() % 16 == 0
+
+
+def moe_grouped(x: torch.Tensor, pair_of: torch.Tensor, offsets: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                w_down: torch.Tensor, act: torch.Tensor, ys: torch.Tensor, top: int) -> torch.Tensor:
+    """Every expert over its rows of the plan, on the tensor cores, the counts read on the device (csrc/moe_tc.cu):
+    act [pairs, ff] = silu(x . gate) * (x . up), ys [pairs, width] = act . down, both in the plan's row order."""
+    _cuda(x, pair_of, offsets, w_gate, w_up, w_down, act, ys)
+    n, width = x.shape
+    E, ff = w_gate.shape[0], w_gate.shape[1]
+    if not all(t.is_contiguous() and t.dtype == torch.bfloat16 for t in (x, w_gate, w_up, w_down, act, ys)) \
+            or act.shape != (n * top, ff) or ys.shape != (n * top, width) or w_down.shape != (E, width, ff) or w_up.shape != w_gate.shape:
+        raise KernelError("moe_grouped: contiguous bfloat16 operands of the sizes the experts have")
+    lib.call("ns_moe_grouped", x.data_ptr(), pair_of.data_ptr(), offsets.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(),
+             w_down.data_ptr(), act.data_ptr(), ys.data_ptr(), E, int(top), width, ff, _stream())
+    return ys
 
 
 def moe_gather(x: torch.Tensor, row_of: torch.Tensor, xs: torch.Tensor, top: int) -> torch.Tensor:

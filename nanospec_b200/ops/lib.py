@@ -60,8 +60,10 @@ _SIGNATURES: dict[str, list] = {
     "ns_attention_latent": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _L, _L, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "ns_attention_latent_tc": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _L, _P, _L, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "ns_cast_f32": [_P, _L, _P, _I, _I, _I, _P],
+    "ns_router_logits": [_P, _L, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_route": [_P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
-    "ns_moe_plan": [_P, _I, _I, _P, _P, _P],
+    "ns_moe_plan": [_P, _I, _I, _P, _P, _P, _P],
+    "ns_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_gather": [_P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_expert_rows": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],

@@ -7,9 +7,11 @@ up with weights from a router.
     the `top` eligible experts of largest s are chosen; weight_k = s_k / (sum of the chosen s + 1e-20) * scale
     y = sum_k weight_k * down_k(silu(gate_k h) * (up_k h))
 
-Two routes, the same numbers up to rounding.  A step of a few tokens (`ROWS_MAX` or fewer, and every step that a CUDA graph
-captures) runs `ops.moe_expert_rows`: the chosen experts' rows are streamed per (token, choice) and nothing comes back to
-the host.  A longer step brings every expert's tokens side by side (`ops.moe_plan`, `ops.moe_gather`), reads the counts
+Three routes, the same numbers up to rounding.  A bfloat16 step (of up to `GROUPED_MAX` tokens when that is set, and every step that a CUDA
+graph captures) lays the (token, choice) pairs out by expert on the device (`ops.moe_plan`) and runs every expert over its
+rows in one tensor-core kernel that reads the counts on the device (`ops.moe_grouped`): each chosen expert's weights are
+read once, nothing comes back to the host.  float32 steps of a few tokens (`ROWS_MAX` or fewer, or captured) run
+`ops.moe_expert_rows`: the chosen experts' rows are streamed per (token, choice).  A longer step brings every expert's tokens side by side (`ops.moe_plan`, `ops.moe_gather`), reads the counts
 on the host, runs each expert that has tokens as the framework's gated product and down product over its run of rows, and
 adds the results per token in the order of the choice (`ops.moe_combine`, float32 sums, one rounding).
 
@@ -26,7 +28,11 @@ from .base import Part, WeightSpec
 from .context import StepContext
 from .registry import register_part
 
-ROWS_MAX = 16  # steps of up to this many tokens stream the chosen experts' rows instead of sorting tokens by expert
+ROWS_MAX = 16      # steps of up to this many tokens stream the chosen experts' rows (float32, or widths that are no multiple of 8)
+# bfloat16 steps of up to this many tokens run every expert over its tokens in one tensor-core kernel (None: every step).  The
+# library products of the sorted route change shape with every step's counts, and the library's choice of a kernel for a
+# shape it has not seen costs the host about 0.6 ms a call: a prompt of 2,048 tokens over 32 experts spent 75 ms there.
+GROUPED_MAX: int | None = None
 
 
 @register_part("feed_forward", "routed_experts")
@@ -73,8 +79,8 @@ class RoutedExperts(Part):
     def route(self, x, ctx: StepContext) -> tuple[torch.Tensor, torch.Tensor]:
         """(chosen experts int32 [N, top], their weights float32 [N, top])"""
         n = x.shape[0]
-        x32 = x if x.dtype == torch.float32 else ops.cast_f32(x, ctx.buffer("router_in", self.hidden, torch.float32))
-        logits = ops.linear(x32, self.w_router, ctx.buffer("router_logits", self.experts, torch.float32))
+        logits = ops.router_logits(x, self.w_router, ctx.buffer("router_logits", self.experts, torch.float32),
+                                   scratch=lambda rows, cols: ctx.buffer("router_in", cols, torch.float32, rows=rows))
         ids = ctx.buffer("expert_ids", self.top, torch.int32)
         weights = ctx.buffer("expert_weights", self.top, torch.float32)
         ops.moe_route(logits, self.groups, self.keep, self.top, self.scale, ids, weights, self.softmax)
@@ -84,11 +90,19 @@ class RoutedExperts(Part):
         n = x.shape[0]
         ids, weights = self.route(x, ctx)
         out = ctx.buffer("branch", self.hidden)
-        if n <= ROWS_MAX or ctx.extras.get("graph") or torch.cuda.is_current_stream_capturing():
-            act = ctx.buffer("expert_act", self.inter, rows=n * self.top)
-            return ops.moe_expert_rows(x, ids, weights, self.w_gate, self.w_up, self.w_down, act, out)
+        captured = bool(ctx.extras.get("graph")) or torch.cuda.is_current_stream_capturing()
         offsets = ctx.buffer("expert_offsets", 1, torch.int32, rows=self.experts + 1).view(-1)
         row_of = ctx.buffer("expert_rows", self.top, torch.int32)
+        if (GROUPED_MAX is None or n <= GROUPED_MAX or captured) and ops.moe_grouped_ok(x, self.hidden, self.inter):
+            pair_of = ctx.buffer("expert_pairs", self.top, torch.int32)
+            ops.moe_plan(ids, self.experts, offsets, row_of, pair_of)
+            act = ctx.buffer("expert_act", self.inter, rows=n * self.top)
+            ys = ctx.buffer("expert_out", self.hidden, rows=n * self.top)
+            ops.moe_grouped(x, pair_of, offsets, self.w_gate, self.w_up, self.w_down, act, ys, self.top)
+            return ops.moe_combine(ys, row_of, weights, out, self.top)
+        if n <= ROWS_MAX or captured:
+            act = ctx.buffer("expert_act", self.inter, rows=n * self.top)
+            return ops.moe_expert_rows(x, ids, weights, self.w_gate, self.w_up, self.w_down, act, out)
         ops.moe_plan(ids, self.experts, offsets, row_of)
         xs = ops.moe_gather(x, row_of, ctx.buffer("expert_in", self.hidden, rows=n * self.top), self.top)
         ys = ctx.buffer("expert_out", self.hidden, rows=n * self.top)

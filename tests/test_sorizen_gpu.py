@@ -145,13 +145,16 @@ def close(got, want, dtype, what="", flips=False):
     """float32: a few roundings against the logits' spread at every position.  bfloat16: the roundings of a bfloat16
     pipeline - small at the median position, never of the size that a wrong window, a lost sink or a wrong page gives.
     `flips`: the model routes tokens to experts, and in bfloat16 a near tie of two scores may fall the other way than in
-    the plain statement: one position in twenty may then be off by any amount."""
+    the plain statement; the token's output then differs outright, and so does what later tokens of its window read.  With
+    several routed layers this touches a fair share of the positions, so three in four must be close (float32, where no
+    tie is near enough to matter, is held at every position; the experts' bfloat16 kernels are held alone, with the
+    choice given)."""
     r = distance(got, want)
     if dtype == F32:
         assert float(r.max()) <= 2e-4, f"{what}: {float(r.max())} at position {int(r.argmax())} (limit 2e-4)"
         return
     q = r.sort().values
-    median, worst = float(q[len(q) // 2]), float(q[int(0.95 * (len(q) - 1))] if flips else q[-1])
+    median, worst = float(q[len(q) // 2]), float(q[int(0.75 * (len(q) - 1))] if flips else q[-1])
     assert (median <= 0.04 or len(q) < 8) and worst <= 0.25, f"{what}: {median:.3f} at the median position, {worst:.3f} at the worst"
 
 
@@ -257,23 +260,60 @@ def test_activation_kernel_alone():
     assert (plain.gelu_erf(z.double()) - plain.gelu_tanh(z.double())).abs().max() > 1e-4  # the two are told apart
 
 
-def test_experts_both_routes_agree(tmp_path):
-    """A step of a few tokens streams the chosen experts' rows; a longer one sorts tokens by expert: the same numbers."""
+def test_experts_every_route_agrees(tmp_path):
+    """Tokens sorted by expert on the host's count (library products per expert), the chosen experts' rows streamed per
+    (token, choice), and every expert over its rows in one tensor-core kernel (bfloat16): the same numbers."""
     from nanospec_b200.parts import experts
 
     cfg = config([layer("latent_attention", moe(experts=6, top=3, ff=24, count=3, keep=2))])
+    big = 1 << 20
     for dtype in (F32, BF16):
         runner, w = make(tmp_path, cfg, seed=4, dtype=dtype)
-        ids = tokens(30, cfg["vocab"], 6)
+        ids = tokens(70, cfg["vocab"], 6)
         want = plain.forward(cfg, w, ids)
-        old = experts.ROWS_MAX
+        old = experts.ROWS_MAX, experts.GROUPED_MAX
         try:
-            for rows_max in (0, 1 << 20):
-                experts.ROWS_MAX = rows_max
-                close(run_cut(runner, 0, ids, [30]), want, dtype, f"experts, ROWS_MAX {rows_max}", flips=True)
-                close(run_cut(runner, 0, ids, [3, 2]), want, dtype, f"experts in portions, ROWS_MAX {rows_max}", flips=True)
+            for rows_max, grouped_max in ((0, 0), (big, 0), (0, big)):
+                experts.ROWS_MAX, experts.GROUPED_MAX = rows_max, grouped_max
+                close(run_cut(runner, 0, ids, [70]), want, dtype, f"experts, limits {rows_max}, {grouped_max}", flips=True)
+                close(run_cut(runner, 0, ids, [40, 3, 2]), want, dtype, f"experts in portions, limits {rows_max}, {grouped_max}", flips=True)
         finally:
-            experts.ROWS_MAX = old
+            experts.ROWS_MAX, experts.GROUPED_MAX = old
+
+
+@pytest.mark.parametrize("experts_n,top,ff,width", [(8, 2, 64, 64), (5, 3, 72, 136), (16, 4, 200, 256)])
+def test_grouped_experts_kernel_alone(experts_n, top, ff, width):
+    """The tensor-core kernel of the grouped experts against float64 on its own operands: experts with no token, with one,
+    and with more than a row tile holds; widths that leave partial tiles."""
+    from nanospec_b200 import ops
+
+    g = torch.Generator().manual_seed(experts_n)
+    n = 90
+    x = (torch.randn(n, width, generator=g)).to(BF16)
+    wg, wu = (torch.randn(experts_n, ff, width, generator=g) / math.sqrt(width)).to(BF16), (torch.randn(experts_n, ff, width, generator=g) / math.sqrt(width)).to(BF16)
+    wd = (torch.randn(experts_n, width, ff, generator=g) / math.sqrt(ff)).to(BF16)
+    ids = torch.stack([torch.randperm(experts_n - 1, generator=g)[:top] + 1 for _ in range(n)]).int()  # expert 0 gets nobody
+    ids[:60, 0] = 1                                                                                      # expert 1 gets many
+    ids[:60, 1:] = torch.stack([torch.randperm(experts_n - 2, generator=g)[:top - 1] + 2 for _ in range(60)]).int()
+    weights = torch.rand(n, top, generator=g)
+    dev = lambda t: t.cuda().contiguous()
+    offsets = torch.empty(experts_n + 1, dtype=torch.int32, device="cuda")
+    row_of, pair_of = torch.empty(n, top, dtype=torch.int32, device="cuda"), torch.empty(n, top, dtype=torch.int32, device="cuda")
+    ops.moe_plan(dev(ids), experts_n, offsets, row_of, pair_of)
+    counts = torch.bincount(ids.flatten().long(), minlength=experts_n)
+    assert offsets.cpu().tolist() == [0] + counts.cumsum(0).tolist()
+    assert torch.equal(pair_of.flatten()[row_of.flatten().long()].cpu(), torch.arange(n * top, dtype=torch.int32))
+    act = torch.empty(n * top, ff, dtype=BF16, device="cuda")
+    ys = torch.empty(n * top, width, dtype=BF16, device="cuda")
+    ops.moe_grouped(dev(x), pair_of, offsets, dev(wg), dev(wu), dev(wd), act, ys, top)
+    out = ops.moe_combine(ys, row_of, dev(weights), torch.empty(n, width, dtype=BF16, device="cuda"), top).float().cpu()
+    want = torch.zeros(n, width, dtype=torch.float64)
+    for t in range(n):
+        for k in range(top):
+            e = int(ids[t, k])
+            h = plain.silu(wg[e].double() @ x[t].double()) * (wu[e].double() @ x[t].double())
+            want[t] += float(weights[t, k]) * (wd[e].double() @ h)
+    assert (out - want).abs().max() <= 0.03 * float(want.abs().max())
 
 
 # ---- windows, sinks, far keys --------------------------------------------------------------------------------------------
