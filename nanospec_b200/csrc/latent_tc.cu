@@ -4,9 +4,9 @@
 // first R features are also the value.  A block takes one token and up to 16 of its heads as the 16 rows of the
 // tensor-core tile - the heads share every key, so a key tile is loaded once for all of them - and walks the token's
 // visible keys 64 at a time:
-//   S = Q K^T     each of the four warps takes 16 of the tile's keys over all D features
-//   softmax       float, running maximum and sum per row; the row statistics of the four warps meet in shared memory
-//   O += P V      each warp takes a quarter of the R value columns over all 64 keys; P goes through shared memory as
+//   S = Q K^T     each of the eight warps takes 8 of the tile's keys over all D features
+//   softmax       float, running maximum and sum per row; the row statistics of the eight warps meet in shared memory
+//   O += P V      each warp takes an eighth of the R value columns over all 64 keys; P goes through shared memory as
 //                 a pair of bfloat16 (the rounded weight and what the rounding dropped, about 16 bits together)
 // When a step has few (token, head group) pairs the keys of a token are split over several blocks, which leave
 // unnormalised partial results in scratch; ns_latent_merge adds them up.  The sink joins the denominator and the
@@ -18,12 +18,13 @@ namespace {
 
 constexpr int kKeysTile = 64;
 constexpr int kRows = 16;
+constexpr int kWarps = 8;
 constexpr int kPStride = kKeysTile + 8;
 constexpr float kLog2e = 1.4426950408889634f;
 
-// UNITS: 16-column units of the value that one warp owns (R / 64, rounded up)
+// UNITS: 16-column units of the value that one warp owns (R / 128, rounded up)
 template <int UNITS>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kWarps * 32)
 attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql_tok, long long ql_head,
                            const __nv_bfloat16* __restrict__ q_rot, long long qr_tok, long long qr_head,
                            const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
@@ -40,8 +41,8 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
     __nv_bfloat16* qs = ks + kKeysTile * KS;                          // [16][KS]
     __nv_bfloat16* ph = qs + kRows * KS;                              // [16][72] rounded weights
     __nv_bfloat16* pl = ph + kRows * kPStride;                        // [16][72] what the rounding dropped
-    float* wmax = reinterpret_cast<float*>(pl + kRows * kPStride);    // [4][16]
-    float* wsum = wmax + 4 * kRows;                                   // [4][16]
+    float* wmax = reinterpret_cast<float*>(pl + kRows * kPStride);    // [warps][16]
+    float* wsum = wmax + kWarps * kRows;                              // [warps][16]
     __shared__ unsigned slots[kKeysTile];
 
     const int n = blockIdx.x, h0 = blockIdx.y * kRows, split = blockIdx.z;
@@ -107,30 +108,23 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
         ns_cp_async_wait<0>();
         __syncthreads();
 
-        // ---- S = Q K^T for this warp's 16 keys
-        float s[2][4];
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) s[t][i] = 0.f;
-        const int kw = warp * 16;
+        // ---- S = Q K^T for this warp's 8 keys
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const int kw = warp * 8;
         for (int d0 = 0; d0 < D; d0 += 16) {
-            uint32_t a[4], b[4];
+            uint32_t a[4], b[2];
             ns_ldmatrix_x4(a, qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * KS + d0 + (lane >> 4) * 8);
-            ns_ldmatrix_x4(b, ks + (kw + (lane & 7) + (lane >> 4) * 8) * KS + d0 + ((lane >> 3) & 1) * 8);
-            ns_mma_bf16(s[0], a, b[0], b[1]);
-            ns_mma_bf16(s[1], a, b[2], b[3]);
+            ns_ldmatrix_x2(b, ks + (kw + (lane & 7)) * KS + d0 + ((lane >> 3) & 1) * 8);
+            ns_mma_bf16(s, a, b[0], b[1]);
         }
         // scale, mask the keys past the end, this warp's row maxima
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = k0 + kw + t * 8 + (lane & 3) * 2 + (i & 1);
-                s[t][i] = key < kend ? s[t][i] * scale2 : -INFINITY;
-                if (i < 2) mx0 = fmaxf(mx0, s[t][i]); else mx1 = fmaxf(mx1, s[t][i]);
-            }
+        for (int i = 0; i < 4; ++i) {
+            const int key = k0 + kw + (lane & 3) * 2 + (i & 1);
+            s[i] = key < kend ? s[i] * scale2 : -INFINITY;
+            if (i < 2) mx0 = fmaxf(mx0, s[i]); else mx1 = fmaxf(mx1, s[i]);
+        }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -141,19 +135,20 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
         }
         __syncthreads();
         const int r0 = lane >> 2, r1 = r0 + 8;
-        const float mn0 = fmaxf(m0, fmaxf(fmaxf(wmax[r0], wmax[kRows + r0]), fmaxf(wmax[2 * kRows + r0], wmax[3 * kRows + r0])));
-        const float mn1 = fmaxf(m1, fmaxf(fmaxf(wmax[r1], wmax[kRows + r1]), fmaxf(wmax[2 * kRows + r1], wmax[3 * kRows + r1])));
+        float mn0 = m0, mn1 = m1;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            mn0 = fmaxf(mn0, wmax[w * kRows + r0]);
+            mn1 = fmaxf(mn1, wmax[w * kRows + r1]);
+        }
         const float c0 = ns_exp2(m0 - mn0), c1 = ns_exp2(m1 - mn1);  // the first tile: 2^(-inf) = 0
         m0 = mn0;
         m1 = mn1;
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const float p0 = ns_exp2(s[t][0] - mn0), p1 = ns_exp2(s[t][1] - mn0);
-            const float p2 = ns_exp2(s[t][2] - mn1), p3 = ns_exp2(s[t][3] - mn1);
-            sum0 += p0 + p1;
-            sum1 += p2 + p3;
-            const int col = kw + t * 8 + (lane & 3) * 2;
+        const float p0 = ns_exp2(s[0] - mn0), p1 = ns_exp2(s[1] - mn0);
+        const float p2 = ns_exp2(s[2] - mn1), p3 = ns_exp2(s[3] - mn1);
+        float sum0 = p0 + p1, sum1 = p2 + p3;
+        {
+            const int col = kw + (lane & 3) * 2;
             *reinterpret_cast<uint32_t*>(ph + r0 * kPStride + col) = ns_pack_bf16(p0, p1);
             *reinterpret_cast<uint32_t*>(ph + r1 * kPStride + col) = ns_pack_bf16(p2, p3);
             *reinterpret_cast<uint32_t*>(pl + r0 * kPStride + col) = ns_pack_bf16_rest(p0, p1);
@@ -168,10 +163,18 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
             wsum[warp * kRows + r1] = sum1;
         }
         __syncthreads();
-        l0 = l0 * c0 + ((wsum[r0] + wsum[kRows + r0]) + (wsum[2 * kRows + r0] + wsum[3 * kRows + r0]));
-        l1 = l1 * c1 + ((wsum[r1] + wsum[kRows + r1]) + (wsum[2 * kRows + r1] + wsum[3 * kRows + r1]));
+        {
+            float t0 = 0.f, t1 = 0.f;  // the warps' sums in their order
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                t0 += wsum[w * kRows + r0];
+                t1 += wsum[w * kRows + r1];
+            }
+            l0 = l0 * c0 + t0;
+            l1 = l1 * c1 + t1;
+        }
 
-        // ---- O += P V over this warp's value columns (units warp, warp + 4, ...)
+        // ---- O += P V over this warp's value columns (units warp, warp + 8, ...)
 #pragma unroll
         for (int u = 0; u < UNITS; ++u)
 #pragma unroll
@@ -187,7 +190,7 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
             ns_ldmatrix_x4(al, pl + prow * kPStride + pcol);
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
-                const int unit = warp + 4 * u;
+                const int unit = warp + kWarps * u;
                 if (unit < n_units) {
                     uint32_t b[4];
                     ns_ldmatrix_x4_trans(b, ks + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + unit * 16 + (lane >> 4) * 8);
@@ -213,7 +216,7 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
         }
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
-            const int unit = warp + 4 * u;
+            const int unit = warp + kWarps * u;
             if (unit >= n_units) continue;
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
@@ -245,7 +248,7 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
     }
 #pragma unroll
     for (int u = 0; u < UNITS; ++u) {
-        const int unit = warp + 4 * u;
+        const int unit = warp + kWarps * u;
         if (unit >= n_units) continue;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
@@ -303,22 +306,21 @@ NS_API int ns_attention_latent_tc(const void* q_lat, long long ql_tok, long long
         NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_latent_tc: the output's strides must be even and the cache 16-byte aligned");
     if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && (!part_o || !part_ml))) NS_FAIL(NS_ERR_ARGUMENT, "ns_attention_latent_tc: n_splits=%d", n_splits);
     const int D = R + r, groups = (H + kRows - 1) / kRows;
-    const size_t smem = ((size_t)(kKeysTile + kRows) * (D + 8) + 2 * kRows * kPStride) * sizeof(__nv_bfloat16) + 2 * 4 * kRows * sizeof(float);
+    const size_t smem = ((size_t)(kKeysTile + kRows) * (D + 8) + 2 * kRows * kPStride) * sizeof(__nv_bfloat16) + 2 * kWarps * kRows * sizeof(float);
     dim3 grid(n_tokens, groups, n_splits);
-    const int units = (R / 16 + 3) / 4;
+    const int units = (R / 16 + kWarps - 1) / kWarps;
 #define NS_LATENT_TC(U)                                                                                                        \
     {                                                                                                                          \
         if (smem > 48 * 1024)                                                                                                  \
             NS_CUDA(cudaFuncSetAttribute(attention_latent_tc_kernel<U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        NS_LAUNCH((attention_latent_tc_kernel<U>), grid, 128, smem, stream, (const __nv_bfloat16*)q_lat, ql_tok, ql_head,        \
+        NS_LAUNCH((attention_latent_tc_kernel<U>), grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q_lat, ql_tok, ql_head,        \
                   (const __nv_bfloat16*)q_rot, qr_tok, qr_head, (const __nv_bfloat16*)cache, block_table, table_stride, token_req, \
                   positions, sink, (const __nv_bfloat16*)gate, gate_tok, (__nv_bfloat16*)out, o_tok, o_head, part_o, part_ml, H, R, \
                   r, page_size, scale, window, n_splits);                                                                       \
     }
     if (units <= 1) NS_LATENT_TC(1)
     else if (units <= 2) NS_LATENT_TC(2)
-    else if (units <= 4) NS_LATENT_TC(4)
-    else NS_LATENT_TC(8)
+    else NS_LATENT_TC(4)
 #undef NS_LATENT_TC
     NS_CHECK_LAUNCH("ns_attention_latent_tc");
     if (n_splits > 1) {

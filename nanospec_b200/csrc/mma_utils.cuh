@@ -26,6 +26,10 @@ __device__ __forceinline__ void ns_ldmatrix_x4(uint32_t (&r)[4], const void* sme
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(ns_smem_u32(smem_row)));
 }
+// two 8x8 matrices; lanes 0-15 give the row addresses (the others' are ignored but must be valid)
+__device__ __forceinline__ void ns_ldmatrix_x2(uint32_t (&r)[2], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(ns_smem_u32(smem_row)));
+}
 __device__ __forceinline__ void ns_ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])

@@ -1043,7 +1043,7 @@ def moe_grouped(x: torch.Tensor, pair_of: torch.Tensor, offsets: torch.Tensor, w
             or act.shape != (n * top, ff) or ys.shape != (n * top, width) or w_down.shape != (E, width, ff) or w_up.shape != w_gate.shape:
         raise KernelError("moe_grouped: contiguous bfloat16 operands of the sizes the experts have")
     lib.call("ns_moe_grouped", x.data_ptr(), pair_of.data_ptr(), offsets.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(),
-             w_down.data_ptr(), act.data_ptr(), ys.data_ptr(), E, int(top), width, ff, _stream())
+             w_down.data_ptr(), act.data_ptr(), ys.data_ptr(), E, int(top), width, ff, (n * int(top)) // E, _stream())
     return ys
 
 
