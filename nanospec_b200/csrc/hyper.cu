@@ -16,7 +16,7 @@
 
 namespace {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;  // the kernels are built for up to 4, 8 and 16 copies
 
 __device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
     const float4 a = *reinterpret_cast<const float4*>(p);
@@ -29,7 +29,7 @@ __device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, int MAXS>
 __global__ void __launch_bounds__(256)
 stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, const float* __restrict__ mix,
                        const float* __restrict__ outw, const float* __restrict__ inw, const float* __restrict__ gain,
@@ -39,10 +39,10 @@ stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, con
     ns_pdl_wait();
     extern __shared__ float u_row[];
     __shared__ float scratch[32];
-    __shared__ float c_mix[kMaxStreams * kMaxStreams], c_out[kMaxStreams], c_in[kMaxStreams];
+    __shared__ float c_mix[MAXS * MAXS], c_out[MAXS], c_in[MAXS];
     const int j = blockIdx.x, tid = threadIdx.x;
     const int row = rows ? rows[j] : j;
-    if (tid < S * S) c_mix[tid] = mix ? mix[tid] : (tid / S == tid % S ? 1.f : 0.f);
+    for (int i = tid; i < S * S; i += blockDim.x) c_mix[i] = mix ? mix[i] : (i / S == i % S ? 1.f : 0.f);
     if (tid < S) {
         c_out[tid] = outw ? outw[tid] : 1.f;
         c_in[tid] = inw ? inw[tid] : 1.f;
@@ -53,9 +53,9 @@ stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, con
     float sum = 0.f;
     // four neighbouring features per thread and turn when rows start on 16 bytes (VEC), one otherwise
     for (int h = tid * VEC; h < hidden; h += blockDim.x * VEC) {
-        float x[kMaxStreams][VEC];
+        float x[MAXS][VEC];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) {
+        for (int s = 0; s < MAXS; ++s) {
             if (s < S) {
                 if constexpr (VEC == 4) {
                     const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)s * hidden + h);
@@ -71,15 +71,15 @@ stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, con
         if (yr) {
             float yv[VEC];
             if constexpr (VEC == 4) ld4(yr + h, yv); else yv[0] = ns_ld(yr, h);
-            float nx[kMaxStreams][VEC];
+            float nx[MAXS][VEC];
 #pragma unroll
-            for (int t = 0; t < kMaxStreams; ++t) {
+            for (int t = 0; t < MAXS; ++t) {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) {
                     float a = 0.f;
                     if (t < S) {
 #pragma unroll
-                        for (int s = 0; s < kMaxStreams; ++s)
+                        for (int s = 0; s < MAXS; ++s)
                             if (s < S) a = fmaf(c_mix[s * S + t], x[s][i], a);
                         a = fmaf(c_out[t], yv[i], a);
                     }
@@ -87,7 +87,7 @@ stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, con
                 }
             }
 #pragma unroll
-            for (int t = 0; t < kMaxStreams; ++t) {
+            for (int t = 0; t < MAXS; ++t) {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) x[t][i] = nx[t][i];
                 if (write_back && t < S) {
@@ -100,7 +100,7 @@ stream_mix_norm_kernel(float* __restrict__ streams, const T* __restrict__ y, con
         for (int i = 0; i < VEC; ++i) {
             float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
+            for (int s = 0; s < MAXS; ++s)
                 if (s < S) u = fmaf(c_in[s], x[s][i], u);
             u_row[h + i] = u;
             sum += centered ? u : u * u;
@@ -190,11 +190,15 @@ NS_API int ns_stream_mix_norm(float* streams, const void* y, const float* mix, c
     // which kernel runs depends on the width and the alignment only, never on the batch
     const bool vec = hidden % 4 == 0 && (((uintptr_t)streams | (uintptr_t)y) % 16 == 0);
     const int threads = hidden >= 1024 ? 256 : 128;
+#define NS_STREAM_LAUNCH_S(T, V, M)                                                                                              \
+    {                                                                                                                            \
+        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<T, V, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+        NS_LAUNCH((stream_mix_norm_kernel<T, V, M>), n_rows, threads, smem, stream, streams, (const T*)y, mix, outw, inw, gain, bias, (T*)out, \
+                  rows, S, hidden, eps, centered, write_back);                                                                   \
+    }
 #define NS_STREAM_LAUNCH(T, V)                                                                                                   \
     {                                                                                                                            \
-        if (smem > 48 * 1024) NS_CUDA(cudaFuncSetAttribute(stream_mix_norm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
-        NS_LAUNCH((stream_mix_norm_kernel<T, V>), n_rows, threads, smem, stream, streams, (const T*)y, mix, outw, inw, gain, bias, (T*)out, \
-                  rows, S, hidden, eps, centered, write_back);                                                                   \
+        if (S <= 4) NS_STREAM_LAUNCH_S(T, V, 4) else if (S <= 8) NS_STREAM_LAUNCH_S(T, V, 8) else NS_STREAM_LAUNCH_S(T, 1, 16)               \
     }
     if (dtype == NS_F32) {
         if (vec) NS_STREAM_LAUNCH(float, 4) else NS_STREAM_LAUNCH(float, 1)
@@ -204,6 +208,7 @@ NS_API int ns_stream_mix_norm(float* streams, const void* y, const float* mix, c
         NS_FAIL(NS_ERR_ARGUMENT, "ns_stream_mix_norm: unknown dtype %d", dtype);
     }
 #undef NS_STREAM_LAUNCH
+#undef NS_STREAM_LAUNCH_S
     NS_CHECK_LAUNCH("ns_stream_mix_norm");
     return NS_OK;
 }

@@ -26,7 +26,7 @@ def _cfg():
               {"type": "latent_attention", "mixer": _mixer(heads=3), "mlp": moe},
               {"type": "latent_attention", "mixer": _mixer(rot_dim=0, rot=None), "mlp": None},
               {"type": "latent_attention", "mixer": _mixer(heads=3), "mlp": moe, "weights_of": 1}]
-    return {"architecture": "Sorizen", "vocab": 61, "width": 24, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.5}, "streams": 3,
+    return {"architecture": "Sorizen", "vocab": 61, "width": 24, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.5}, "streams": 2,
             "layers": layers}
 
 
@@ -34,7 +34,7 @@ def test_round_trip_and_registry():
     cfg = SorizenConfig.from_hf(_cfg())
     assert SorizenConfig.from_hf(cfg.to_hf()) == cfg
     assert resolve_architecture(_cfg()).name == "Sorizen"
-    assert cfg.streams == 3 and cfg.embedding_scale == 2.5 and cfg.layers[3].weights_of == 1
+    assert cfg.streams == 2 and cfg.embedding_scale == 2.5 and cfg.layers[3].weights_of == 1
     plain_stream = _cfg()
     del plain_stream["streams"]
     assert SorizenConfig.from_hf(plain_stream).streams is None

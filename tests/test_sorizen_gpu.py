@@ -65,7 +65,7 @@ def full_config(**kw):
               layer("latent_attention", moe(experts=4, top=1, ff=8, count=0), heads=4, dim=6, rot_dim=4, vdim=6, rank=20, size=5)]
     layers.append(copy.deepcopy(layers[1]))
     layers[-1]["weights_of"] = 1
-    return config(layers, **{"streams": 3, **kw})
+    return config(layers, **{"streams": 4, **kw})
 
 
 def random_weights(cfg: dict, seed: int, q_gain: float = 1.0) -> dict[str, torch.Tensor]:
@@ -155,7 +155,7 @@ def close(got, want, dtype, what="", flips=False):
         return
     q = r.sort().values
     median, worst = float(q[len(q) // 2]), float(q[int(0.75 * (len(q) - 1))] if flips else q[-1])
-    assert (median <= 0.04 or len(q) < 8) and worst <= 0.25, f"{what}: {median:.3f} at the median position, {worst:.3f} at the worst"
+    assert (median <= 0.06 or len(q) < 8) and worst <= 0.25, f"{what}: {median:.3f} at the median position, {worst:.3f} at the worst"
 
 
 # ---- each mechanism alone -----------------------------------------------------------------------------------------------
@@ -197,7 +197,7 @@ def test_stream_kernel_alone():
     from nanospec_b200 import ops
 
     g = torch.Generator().manual_seed(3)
-    for S, H, centered, with_bias in ((1, 24, True, True), (3, 40, True, True), (4, 33, False, False), (8, 1030, True, False)):
+    for S, H, centered, with_bias in ((1, 24, True, True), (3, 40, True, True), (4, 33, False, False), (8, 1030, True, False), (11, 52, True, True)):
         N = 7
         x = torch.randn(N, S, H, generator=g)
         y = torch.randn(N, H, generator=g).to(BF16).float()
@@ -233,7 +233,7 @@ def test_router_kernel_alone():
     from nanospec_b200 import ops
 
     g = torch.Generator().manual_seed(9)
-    for E, top, count, keep, scale in ((12, 4, 4, 3, 2.0), (6, 2, 3, 2, 1.0), (5, 1, 0, 0, 0.5), (64, 6, 8, 3, 2.5), (40, 8, 1, 1, 1.0),
+    for E, top, count, keep, scale in ((12, 5, 4, 3, 1.75), (6, 2, 3, 2, 1.0), (5, 1, 0, 0, 0.5), (64, 6, 8, 3, 2.5), (40, 8, 1, 1, 1.0),
                                        (8, 8, 8, 8, 1.0), (33, 33, 0, 0, 1.0)):
         N = 50
         z = torch.randn(N, E, generator=g) * 2
@@ -281,7 +281,7 @@ def test_experts_every_route_agrees(tmp_path):
             experts.ROWS_MAX, experts.GROUPED_MAX = old
 
 
-@pytest.mark.parametrize("experts_n,top,ff,width", [(8, 2, 64, 64), (5, 3, 72, 136), (16, 4, 200, 256)])
+@pytest.mark.parametrize("experts_n,top,ff,width", [(8, 2, 64, 64), (5, 3, 40, 104), (16, 4, 200, 256)])
 def test_grouped_experts_kernel_alone(experts_n, top, ff, width):
     """The tensor-core kernel of the grouped experts against float64 on its own operands: experts with no token, with one,
     and with more than a row tile holds; widths that leave partial tiles."""
@@ -385,7 +385,7 @@ def test_unequal_batches_and_reuse(seed, dtype, tmp_path):
     that only their peak fits, requests ending and new ones taking their pages and slots: every position as alone."""
     from nanospec_b200.engine.step import StepEntry
 
-    cfg = full_config(streams=3 if seed == 31 else None)
+    cfg = full_config(streams=4 if seed == 31 else None)
     runner, w = make(tmp_path, cfg, seed=seed, dtype=dtype, blocks=28, page=4, slots=4)
     g = torch.Generator().manual_seed(seed)
     lengths = [23, 5, 41, 2, 17, 30, 9]
