@@ -9,6 +9,7 @@
 //                      Ties go to the lower index.
 //   ns_moe_plan        counts per expert, their running offsets, and for every (token, choice) its row in the
 //                      order that has each expert's tokens side by side
+//   ns_moe_pad_rows    the same rows in a layout where every expert owns a fixed number of rows (for one batched product)
 //   ns_moe_gather      x rows into that order;  ns_moe_combine   out[n] = sum_k weight[n, k] * y[row(n, k)] in float
 //   ns_moe_expert_rows the experts themselves for a few tokens, no host round trip: one block row per (token,
 //                      choice) streams the chosen expert's gate and up rows, then its down rows
@@ -181,6 +182,17 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict
     }
 }
 
+// rows of the plan moved to a layout in which every expert owns `capacity` rows: row = expert * capacity + rank in the expert
+__global__ void moe_pad_rows_kernel(const int* __restrict__ ids, const int* __restrict__ offsets, int* __restrict__ row_of, int n_pairs,
+                                    int capacity) {
+    ns_pdl_launch_dependents();
+    ns_pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int e = ids[i];
+    row_of[i] = e * capacity + (row_of[i] - offsets[e]);
+}
+
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_of, T* __restrict__ xs, int top,
                                   int width) {
@@ -345,6 +357,13 @@ NS_API int ns_moe_plan(const int* ids, int n_pairs, int E, int* offsets, int* ro
     if (E < 1 || E > kMaxExperts) NS_FAIL(NS_ERR_UNSUPPORTED, "ns_moe_plan: %d experts (at most %d)", E, kMaxExperts);
     NS_LAUNCH(moe_plan_kernel, 1, 1024, 0, stream, ids, n_pairs, E, offsets, row_of, pair_of);
     NS_CHECK_LAUNCH("ns_moe_plan");
+    return NS_OK;
+}
+
+NS_API int ns_moe_pad_rows(const int* ids, const int* offsets, int* row_of, int n_pairs, int capacity, cudaStream_t stream) {
+    if (n_pairs <= 0) return NS_OK;
+    NS_LAUNCH(moe_pad_rows_kernel, (n_pairs + 255) / 256, 256, 0, stream, ids, offsets, row_of, n_pairs, capacity);
+    NS_CHECK_LAUNCH("ns_moe_pad_rows");
     return NS_OK;
 }
 

@@ -1047,11 +1047,20 @@ def moe_grouped(x: torch.Tensor, pair_of: torch.Tensor, offsets: torch.Tensor, w
     return ys
 
 
+def moe_pad_rows(ids: torch.Tensor, offsets: torch.Tensor, row_of: torch.Tensor, capacity: int) -> None:
+    """row_of, in place: from the plan's rows to a layout in which expert e owns rows e * capacity .. (e + 1) * capacity - 1."""
+    _cuda(ids, offsets, row_of)
+    for t, name in ((ids, "ids"), (offsets, "offsets"), (row_of, "row_of")):
+        _i32(t, name)
+    lib.call("ns_moe_pad_rows", ids.data_ptr(), offsets.data_ptr(), row_of.data_ptr(), ids.numel(), int(capacity), _stream())
+
+
 def moe_gather(x: torch.Tensor, row_of: torch.Tensor, xs: torch.Tensor, top: int) -> torch.Tensor:
+    """xs[row_of[n, k]] = x[n]; xs may hold more rows than pairs (a padded layout): the others are left as they are."""
     _cuda(x, row_of, xs)
     n, width = x.shape
-    if xs.shape != (n * top, width) or xs.dtype != x.dtype or not (x.is_contiguous() and xs.is_contiguous()):
-        raise KernelError("moe_gather: xs [N * top, width] of x's dtype, contiguous")
+    if xs.shape[0] < n * top or xs.shape[1] != width or xs.dtype != x.dtype or not (x.is_contiguous() and xs.is_contiguous()):
+        raise KernelError("moe_gather: xs [at least N * top, width] of x's dtype, contiguous")
     lib.call("ns_moe_gather", x.data_ptr(), row_of.data_ptr(), xs.data_ptr(), n, int(top), width, dtype_code(x.dtype), _stream())
     return xs
 
@@ -1059,8 +1068,8 @@ def moe_gather(x: torch.Tensor, row_of: torch.Tensor, xs: torch.Tensor, top: int
 def moe_combine(ys: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> torch.Tensor:
     _cuda(ys, row_of, weights, out)
     n, width = out.shape
-    if ys.shape != (n * top, width) or ys.dtype != out.dtype or not (ys.is_contiguous() and out.is_contiguous()):
-        raise KernelError("moe_combine: ys [N * top, width] of out's dtype, contiguous")
+    if ys.shape[0] < n * top or ys.shape[1] != width or ys.dtype != out.dtype or not (ys.is_contiguous() and out.is_contiguous()):
+        raise KernelError("moe_combine: ys [at least N * top, width] of out's dtype, contiguous")
     lib.call("ns_moe_combine", ys.data_ptr(), row_of.data_ptr(), weights.data_ptr(), out.data_ptr(), n, int(top), width,
              dtype_code(out.dtype), _stream())
     return out

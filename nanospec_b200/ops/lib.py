@@ -64,6 +64,7 @@ _SIGNATURES: dict[str, list] = {
     "ns_moe_route": [_P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
     "ns_moe_plan": [_P, _I, _I, _P, _P, _P, _P],
     "ns_moe_grouped": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "ns_moe_pad_rows": [_P, _P, _P, _I, _I, _P],
     "ns_moe_gather": [_P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ns_moe_expert_rows": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
