@@ -99,10 +99,11 @@ attention_latent_tc_kernel(const __nv_bfloat16* __restrict__ q_lat, long long ql
             slots[tid] = key < kend ? (unsigned)bt[key / page_size] * (unsigned)page_size + (unsigned)(key % page_size) : 0xffffffffu;
         }
         __syncthreads();
-        for (int c = tid; c < kKeysTile * chunks; c += blockDim.x) {
-            const int row = c / chunks, ch = c - row * chunks;
+        // a warp copies whole rows, its lanes the 16-byte pieces of a row: no division per piece
+        for (int row = warp; row < kKeysTile; row += kWarps) {
             const unsigned s = slots[row];
-            ns_cp_async16(ks + row * KS + ch * 8, cache + (s == 0xffffffffu ? 0 : (size_t)s * D + ch * 8), s != 0xffffffffu);
+            const __nv_bfloat16* src = cache + (s == 0xffffffffu ? 0 : (size_t)s * D);
+            for (int ch = lane; ch < chunks; ch += 32) ns_cp_async16(ks + row * KS + ch * 8, src + ch * 8, s != 0xffffffffu);
         }
         ns_cp_async_commit();
         ns_cp_async_wait<0>();
