@@ -273,10 +273,17 @@ def test_experts_every_route_agrees(tmp_path):
         want = plain.forward(cfg, w, ids)
         old = experts.ROWS_MAX, experts.GROUPED_MAX
         try:
+            whole = []
             for rows_max, grouped_max in ((0, 0), (big, 0), (0, big)):
                 experts.ROWS_MAX, experts.GROUPED_MAX = rows_max, grouped_max
-                close(run_cut(runner, 0, ids, [70]), want, dtype, f"experts, limits {rows_max}, {grouped_max}", flips=True)
+                whole.append(run_cut(runner, 0, ids, [70]))
+                close(whole[-1], want, dtype, f"experts, limits {rows_max}, {grouped_max}", flips=True)
                 close(run_cut(runner, 0, ids, [40, 3, 2]), want, dtype, f"experts in portions, limits {rows_max}, {grouped_max}", flips=True)
+            # the routes share the router's kernel and its input (the model's one routed layer is its last sublayer), so they
+            # choose alike and must agree with one another at every position, near ties or not
+            for other in whole[1:]:
+                r = distance(other, whole[0])
+                assert float(r.max()) <= (1e-5 if dtype == F32 else 0.02), f"two routes differ by {float(r.max())} at position {int(r.argmax())}"
         finally:
             experts.ROWS_MAX, experts.GROUPED_MAX = old
 
