@@ -1,7 +1,7 @@
 // A residual stream held as several copies (hyper-connections), and the embedding that opens it.
 //
 // A token's row holds S streams of `hidden` floats, one after another.  Around a sublayer with
-// coefficients in[S], out[S] and mix[S, S] (indexed [from, to]) the streams move as
+// coefficients in[S], out[S] and mix[S, S] (first index: the copy read; second: the copy written) the streams move as
 //     u   = sum_s in[s] x_s                      what the sublayer's norm reads
 //     y   = sublayer(norm(u))
 //     x_t = sum_s mix[s, t] x_s + out[t] y       all t at once, from the old streams

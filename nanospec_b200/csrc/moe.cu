@@ -3,9 +3,9 @@
 //
 //   ns_cast_f32        rows of the compute type as float (the router's input: its logits are a float product)
 //   ns_router_logits   the router's float product for a few tokens (longer steps: ns_cast_f32 and the float GEMM)
-//   ns_moe_route       scores = sigmoid(logits) (or softmax); experts in `groups` equal runs of neighbours, a group's
-//                      score the sum of its two largest scores, only the best `keep` groups eligible; the `top`
-//                      eligible experts with the largest scores; weights = score / (sum of the chosen + 1e-20) * scale.
+//   ns_moe_route       scores = sigmoid(logits) (or softmax); consecutive experts form `groups` groups of equal size, ranked by
+//                      the top-2 sum of their scores; all but the `keep` highest-ranked groups are barred; then the `top`
+//                      highest-scoring experts that are not barred; weights = score / (sum of the chosen + 1e-20) * scale.
 //                      Ties go to the lower index.
 //   ns_moe_plan        counts per expert, their running offsets, and for every (token, choice) its row in the
 //                      order that has each expert's tokens side by side

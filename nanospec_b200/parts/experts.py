@@ -2,8 +2,8 @@
 up with weights from a router.
 
     z = W_router h   (a float32 product in every mode)          s = sigmoid(z)   ("score": "softmax" for a softmax over z)
-    experts lie in `groups` equal runs of neighbours; a group's score is the sum of its two largest s, and only experts of
-    the best `keep` groups can be chosen (groups <= 1: every expert can)
+    experts e * per .. (e + 1) * per - 1 form group e (`groups` of them, per = experts / groups); group score = top-2 sum of its s
+    (its one s when per is 1); the `keep` groups of highest score stay eligible, the rest are barred (groups <= 1: none barred)
     the `top` eligible experts of largest s are chosen; weight_k = s_k / (sum of the chosen s + 1e-20) * scale
     y = sum_k weight_k * down_k(silu(gate_k h) * (up_k h))
 

@@ -3,7 +3,7 @@ small learned coefficients.
 
 The stream of a step is one float32 tensor [N, streams * hidden] (a token's copies side by side); the embedding opens it
 with every copy equal (`copies` of the "table" embedding).  Sublayer q of a layer, with coefficients in[S], out[S] and
-mix[S, S] (indexed [from, to]):
+mix[S, S] (first index: the copy read; second: the copy written):
 
     u   = sum_s in[s] x_s
     y   = sublayer(norm(u))

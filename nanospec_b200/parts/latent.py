@@ -1,8 +1,8 @@
 """Attention whose cache holds one latent vector per token instead of keys and values per head.
 
     q      = W_q h                          per head [dim plain | rot_dim rotated]
-    [c|kr] = W_dkv h                        c: rank features, RMS-normed with a gain; kr: rot_dim features, one rotated key
-                                            part shared by all heads
+    [c|kr] = W_dkv h                        c: rank features, RMS-normed with a gain; kr: rot_dim features, a single
+                                            rotated key vector that every head uses
     key_h  = [W_uk,h c | kr],  value_h = W_uv,h c
     score  = (q_plain . key_plain + q_rot . kr) * scale,   causal, inside a window when one is set
     softmax, optionally with a learned sink per head in the denominator; optionally head h's output times
